@@ -19,7 +19,7 @@ CC_MAX_DIMS = 4
 F32, F16, Q4_0, Q4_1, Q5_0, Q5_1, Q8_0, Q8_1 = 0, 1, 2, 3, 6, 7, 8, 9
 Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, Q8_K = 10, 11, 12, 13, 14, 15
 I32, BF16 = 26, 30
-ACT_NONE, ACT_SILU, ACT_GELU_TANH, ACT_SWISH = 0, 1, 2, 3
+ACT_NONE, ACT_SILU, ACT_GELU_TANH, ACT_SWISH, ACT_SIGMOID = 0, 1, 2, 3, 4
 ROUTE_SOFTMAX, ROUTE_SIGMOID = 0, 1
 ROPE_LLAMA, ROPE_NEOX = 0, 1
 
@@ -96,6 +96,28 @@ CMR_WEIGHT_FIELDS = ("norm1", "h_stack", "dq_norm", "uq", "dkv_norm", "uk", "uv"
 
 class cmr_layer_weights(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in CMR_WEIGHT_FIELDS]
+
+
+class cvr_layer_config(C.Structure):            # include/crabml_vuzinex.h
+    _fields_ = [(n, C.c_int32) for n in ("mixer", "heads", "kv_heads", "dim", "vdim", "window", "block", "left_gate")] + [("scale", C.c_float), ("rot_mag", C.c_float)] + \
+               [(n, C.c_int32) for n in ("right", "r_heads", "r_dim", "r_vdim", "r_rank")] + \
+               [(n, C.c_float) for n in ("gate_cap", "tau", "r_q_scale", "left_scale", "right_scale")] + \
+               [(n, C.c_int32) for n in ("s_heads", "s_vdim", "s_state", "s_groups", "s_conv", "s_norm_groups", "ff")]
+
+
+class cvr_config(C.Structure):
+    _fields_ = [("n_layers", C.c_int32), ("width", C.c_int32), ("vocab", C.c_int32), ("norm_eps", C.c_float), ("residual_mult", C.c_float), ("logit_scale", C.c_float)] + \
+               [(n, C.c_int32) for n in ("loop_start", "loop_stop", "loop_times")] + [(n, C.c_int64) for n in ("hash_buckets", "hash_mul_prev", "hash_mul_cur")] + \
+               [("chunk", C.c_int32), ("max_seq", C.c_int32)]
+
+
+CVR_WEIGHT_FIELDS = ("norm_a", "norm_b", "norm_c", "norm_d", "h_stack", "h_bias", "q_norm", "k_norm", "sink", "rot_freq", "left_o", "right_norm", "right_o", "gate_bias_i",
+                     "gate_bias_f", "decay_up", "decay_bias", "in", "conv", "conv_bias", "dt_bias", "a_log", "d_skip", "s_norm", "s_o", "gate_up", "gate_up_bias", "down",
+                     "down_bias")
+
+
+class cvr_layer_weights(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in CVR_WEIGHT_FIELDS]
 
 
 class cc_route_params(C.Structure):              # include/crabml_seqops.h
@@ -218,6 +240,18 @@ def load_library(build_if_missing: bool = True):
         "cc_head_concat_shared": (i32, [vp, pv, pv, i32, i32, i32, pp]),
         "cc_moe_route_ex": (i32, [vp, pv, pv, pv, C.POINTER(cc_route_params), pp, pp]),
         "cc_moe_experts_glu": (i32, [vp, pv, pv, pv, pv, pv, pv, i32, i32, C.POINTER(cc_glu_params), pp]),
+        "cc_rms_norm_gain_mult": (i32, [vp, pv, pv, pv, f32, f32]),
+        "cc_gated_group_rms_norm": (i32, [vp, pv, pv, pv, pv, i32, f32, i32]),
+        "cc_glu_halves": (i32, [vp, pv, pv, i32, pp]),
+        "cc_add_row_bias": (i32, [vp, pv, pv]),
+        "cc_scaled_sum": (i32, [vp, pv, pv, f32, pv, f32]),
+        "cc_pair_hash_rows_add": (i32, [vp, pv, pv, C.POINTER(i64), i32, i32, pv, i64, i64, i64]),
+        "cc_short_conv_bias": (i32, [vp, pv, pv, pv, pv, i32, pp]),
+        "cc_masked_attention": (i32, [vp, pv, pv, pv, i64, i32, i32, i32, i32, i32, i32, f32, pv, pp]),
+        "cc_matrix_memory": (i32, [vp, pv, pv, pv, pv, pv, pv, pv, f32, f32, pv, pv, i32, i32, i32, pp]),
+        "cc_decayed_linear_attention": (i32, [vp, pv, pv, pv, pv, pv, f32, f32, pv, i32, i32, i32, pp]),
+        "cc_state_space_scan": (i32, [vp, pv, pv, pv, pv, pv, pv, i32, i32, i32, i32, pp]),
+        "cvr_runner_create": (i32, [vp, C.POINTER(cvr_config), C.POINTER(cvr_layer_config), C.POINTER(cvr_layer_weights), vp, vp, vp, vp, pp]),
         "csr_runner_destroy": (None, [vp]),
         "csr_runner_last_error": (C.c_char_p, [vp]),
         "csr_last_create_error": (C.c_char_p, []),

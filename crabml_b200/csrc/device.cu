@@ -280,7 +280,7 @@ static int64_t prod(const int64_t* shape, int ndim) {
 extern "C" CC_API int cc_tensor_alloc(cc_device* dev, const int64_t* shape, int32_t ndim, int32_t t, cc_buf** out) {
     if (!dev || !shape || !out || ndim < 1 || ndim > CC_MAX_DIMS) return cc_fail(dev, CC_ERR_ARG, "cc_tensor_alloc: bad argument");
     CC_ENTER(dev);
-    CC_REQUIRE(dev, t == CC_F32 || t == CC_F16, "only f32/f16 is supported");   // cpu_tensor.rs:139-141
+    CC_REQUIRE(dev, t == CC_F32 || t == CC_F16 || t == CC_I32, "only f32/f16 is supported");   // cpu_tensor.rs:139-141; I32: index state of the sequence ops
     // F32 is zero-filled (vec![0.0; n]); F16 is uninitialised in the reference (buf_f16.rs:23-28), zeroed here
     return cc_new_activation(dev, prod(shape, ndim), t, true, out);
 }

@@ -33,7 +33,9 @@ __device__ __forceinline__ float seq_silu(float z) { return z / (1.0f + expf(-z)
 __device__ __forceinline__ float seq_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float seq_softplus(float z) { return fmaxf(z, 0.0f) + log1pf(expf(-fabsf(z))); }
 __device__ __forceinline__ float seq_gelu_tanh(float z) { return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
-__device__ __forceinline__ float seq_act(float z, int act) { return act == CC_ACT_SILU ? seq_silu(z) : act == CC_ACT_GELU_TANH ? seq_gelu_tanh(z) : z; }
+__device__ __forceinline__ float seq_act(float z, int act) {
+    return act == CC_ACT_SILU ? seq_silu(z) : act == CC_ACT_GELU_TANH ? seq_gelu_tanh(z) : act == CC_ACT_SIGMOID ? seq_sigmoid(z) : z;
+}
 
 extern "C" CC_API int cc_tensor_zero(cc_device* dev, const cc_view* x) {
     SEQ_ENTER(dev, "tensor_zero");
@@ -47,7 +49,7 @@ extern "C" CC_API int cc_tensor_zero(cc_device* dev, const cc_view* x) {
 // ---- norms --------------------------------------------------------------------------------------------------------------------
 // one warp per row: lane-strided sum of squares, butterfly, then the scaled write
 __global__ void rms_norm_gain_kernel(float* __restrict__ dst, const float* __restrict__ y, const float* __restrict__ gain, int gain_n, int rows, int cols,
-                                     float eps, int accumulate) {
+                                     float eps, int accumulate, float mult) {
     const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (r >= rows) return;
     const float* yr = y + (int64_t)r * cols;
@@ -57,43 +59,65 @@ __global__ void rms_norm_gain_kernel(float* __restrict__ dst, const float* __res
     const float inv = 1.0f / sqrtf(ss / (float)cols + eps);
     float* dr = dst + (int64_t)r * cols;
     for (int c = lane; c < cols; c += 32) {
-        const float v = yr[c] * inv * gain[gain_n == 1 ? 0 : c];
+        const float v = yr[c] * inv * gain[gain_n == 1 ? 0 : c] * mult;
         dr[c] = accumulate ? dr[c] + v : v;
     }
 }
-extern "C" CC_API int cc_rms_norm_gain(cc_device* dev, const cc_view* dst, const cc_view* y, const cc_view* gain, float eps, int32_t accumulate) {
+static int rms_norm_gain_impl(cc_device* dev, const cc_view* dst, const cc_view* y, const cc_view* gain, float eps, int32_t accumulate, float mult) {
     SEQ_ENTER(dev, "rms_norm_gain");
     SEQ_F32(dev, dst, "rms_norm_gain dst"); SEQ_F32(dev, y, "rms_norm_gain y"); SEQ_F32(dev, gain, "rms_norm_gain gain");
     CC_REQUIRE(dev, dst->ndim == 2 && y->ndim == 2 && dst->shape[0] == y->shape[0] && dst->shape[1] == y->shape[1], "rms_norm_gain: dst and y must be [rows, cols]");
     const int64_t rows = y->shape[0], cols = y->shape[1], gn = view_len(gain);
     CC_REQUIRE(dev, gn == 1 || gn == cols, "rms_norm_gain: gain has %lld elements, need 1 or %lld", (long long)gn, (long long)cols);
     if (rows == 0) return CC_OK;
-    rms_norm_gain_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, dev->stream>>>(fptr(dst), fptr(y), fptr(gain), (int)gn, (int)rows, (int)cols, eps, accumulate);
+    rms_norm_gain_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, dev->stream>>>(fptr(dst), fptr(y), fptr(gain), (int)gn, (int)rows, (int)cols, eps, accumulate, mult);
     CC_LAUNCH_CHECK(dev);
     return CC_OK;
 }
+extern "C" CC_API int cc_rms_norm_gain(cc_device* dev, const cc_view* dst, const cc_view* y, const cc_view* gain, float eps, int32_t accumulate) {
+    return rms_norm_gain_impl(dev, dst, y, gain, eps, accumulate, 1.0f);
+}
+extern "C" CC_API int cc_rms_norm_gain_mult(cc_device* dev, const cc_view* dst, const cc_view* y, const cc_view* gain, float eps, float mult) {
+    return rms_norm_gain_impl(dev, dst, y, gain, eps, 1, mult);
+}
 
 // one warp per (row, head)
-__global__ void gated_head_rms_norm_kernel(float* __restrict__ x, const float* __restrict__ gate, const float* __restrict__ w, int64_t n_units, int hs, float eps, int act) {
+// w_heads: how many heads have weights of their own (1: one vector for all)
+__global__ void gated_head_rms_norm_kernel(float* __restrict__ x, const float* __restrict__ gate, const float* __restrict__ w, int64_t n_units, int hs, float eps, int act,
+                                           int w_heads) {
     const int64_t u = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (u >= n_units) return;
     float* xr = x + u * hs;
-    const float* gr = gate + u * hs;
+    const float* gr = gate ? gate + u * hs : nullptr;
+    const float* wr = w ? w + (u % w_heads) * hs : nullptr;
     float ss = 0.0f;
     for (int c = lane; c < hs; c += 32) ss = fmaf(xr[c], xr[c], ss);
     ss = warp_sum(ss);
     const float inv = 1.0f / sqrtf(ss / (float)hs + eps);
-    for (int c = lane; c < hs; c += 32) xr[c] = xr[c] * inv * w[c] * seq_act(gr[c], act);
+    for (int c = lane; c < hs; c += 32) {
+        float v = xr[c] * inv;
+        if (wr) v *= wr[c];
+        if (gr) v *= seq_act(gr[c], act);
+        xr[c] = v;
+    }
 }
 extern "C" CC_API int cc_gated_head_rms_norm(cc_device* dev, const cc_view* x, const cc_view* gate, const cc_view* w, int32_t head_size, float eps, int32_t gate_act) {
     SEQ_ENTER(dev, "gated_head_rms_norm");
-    SEQ_F32(dev, x, "gated_head_rms_norm x"); SEQ_F32(dev, gate, "gated_head_rms_norm gate"); SEQ_F32(dev, w, "gated_head_rms_norm w");
+    SEQ_F32(dev, x, "gated_head_rms_norm x");
+    if (gate) SEQ_F32(dev, gate, "gated_head_rms_norm gate");
+    if (w) SEQ_F32(dev, w, "gated_head_rms_norm w");
     const int64_t n = view_len(x);
-    CC_REQUIRE(dev, head_size > 0 && n % head_size == 0 && view_len(gate) == n && view_len(w) == head_size, "gated_head_rms_norm: shapes do not fit head_size %d", head_size);
+    CC_REQUIRE(dev, head_size > 0 && n % head_size == 0 && (!gate || view_len(gate) == n), "gated_head_rms_norm: shapes do not fit head_size %d", head_size);
+    int w_heads = 1;
+    if (w && view_len(w) != head_size) {
+        CC_REQUIRE(dev, x->ndim == 2 && view_len(w) == x->shape[1], "gated_head_rms_norm: w must have head_size elements or one per column");
+        w_heads = (int)(x->shape[1] / head_size);
+    }
     const int64_t units = n / head_size;
     if (!units) return CC_OK;
-    gated_head_rms_norm_kernel<<<(unsigned)((units + 7) / 8), 256, 0, dev->stream>>>(fptr(x), fptr(gate), fptr(w), units, head_size, eps, gate_act);
+    gated_head_rms_norm_kernel<<<(unsigned)((units + 7) / 8), 256, 0, dev->stream>>>(fptr(x), gate ? fptr(gate) : nullptr, w ? fptr(w) : nullptr, units, head_size, eps, gate_act,
+                                                                                    w_heads);
     CC_LAUNCH_CHECK(dev);
     return CC_OK;
 }
@@ -112,11 +136,110 @@ extern "C" CC_API int cc_glu_inplace(cc_device* dev, const cc_view* gate, const 
     CC_LAUNCH_CHECK(dev);
     return CC_OK;
 }
+// gate | up side by side in one product's rows
+__global__ void glu_halves_kernel(const float* __restrict__ src, const float* __restrict__ bias, float* __restrict__ out, int64_t n, int ff, int act) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int64_t r = i / ff;
+    const int c = (int)(i - r * ff);
+    float g = src[r * 2 * ff + c], u = src[r * 2 * ff + ff + c];
+    if (bias) { g += bias[c]; u += bias[ff + c]; }
+    out[i] = seq_act(g, act) * u;
+}
+extern "C" CC_API int cc_glu_halves(cc_device* dev, const cc_view* src, const cc_view* bias, int32_t act, cc_buf** out) {
+    SEQ_ENTER(dev, "glu_halves");
+    if (!out) return cc_fail(dev, CC_ERR_ARG, "glu_halves: out is NULL");
+    SEQ_F32(dev, src, "glu_halves src");
+    CC_REQUIRE(dev, src->ndim == 2 && src->shape[1] % 2 == 0, "glu_halves: src must be [rows, 2 * ff]");
+    const int64_t rows = src->shape[0], ff = src->shape[1] / 2;
+    if (bias) { SEQ_F32(dev, bias, "glu_halves bias"); CC_REQUIRE(dev, view_len(bias) == 2 * ff, "glu_halves: the bias needs one number per column of src"); }
+    cc_buf* o = nullptr;
+    int rc = cc_new_activation(dev, rows * ff, CC_F32, false, &o);
+    if (rc) return rc;
+    *out = o;
+    const int64_t n = rows * ff;
+    if (!n) return CC_OK;
+    glu_halves_kernel<<<(unsigned)((n + 255) / 256), 256, 0, dev->stream>>>(fptr(src), bias ? fptr(bias) : nullptr, (float*)o->base, n, (int)ff, act);
+    CC_LAUNCH_CHECK(dev);
+    return CC_OK;
+}
+__global__ void add_row_bias_kernel(float* __restrict__ x, const float* __restrict__ b, int64_t n, int cols) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] += b[i % cols];
+}
+extern "C" CC_API int cc_add_row_bias(cc_device* dev, const cc_view* x, const cc_view* bias) {
+    SEQ_ENTER(dev, "add_row_bias");
+    SEQ_F32(dev, x, "add_row_bias x"); SEQ_F32(dev, bias, "add_row_bias bias");
+    CC_REQUIRE(dev, x->ndim == 2 && view_len(bias) == x->shape[1], "add_row_bias: x must be [rows, cols] and bias [cols]");
+    const int64_t n = view_len(x);
+    if (!n) return CC_OK;
+    add_row_bias_kernel<<<(unsigned)((n + 255) / 256), 256, 0, dev->stream>>>(fptr(x), fptr(bias), n, (int)x->shape[1]);
+    CC_LAUNCH_CHECK(dev);
+    return CC_OK;
+}
+__global__ void scaled_sum_kernel(float* __restrict__ dst, const float* __restrict__ a, float sa, const float* __restrict__ b, float sb, int64_t n) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = sa * a[i] + sb * b[i];
+}
+extern "C" CC_API int cc_scaled_sum(cc_device* dev, const cc_view* dst, const cc_view* a, float sa, const cc_view* b, float sb) {
+    SEQ_ENTER(dev, "scaled_sum");
+    SEQ_F32(dev, dst, "scaled_sum dst"); SEQ_F32(dev, a, "scaled_sum a"); SEQ_F32(dev, b, "scaled_sum b");
+    const int64_t n = view_len(dst);
+    CC_REQUIRE(dev, view_len(a) == n && view_len(b) == n, "scaled_sum: sizes differ");
+    if (!n) return CC_OK;
+    scaled_sum_kernel<<<(unsigned)((n + 255) / 256), 256, 0, dev->stream>>>(fptr(dst), fptr(a), sa, fptr(b), sb, n);
+    CC_LAUNCH_CHECK(dev);
+    return CC_OK;
+}
+
+// ---- a second embedding row chosen by a hash of the token pair ------------------------------------------------------------------------
+// one thread per (token, column); the hash is taken in 64-bit integers
+__global__ void pair_hash_rows_add_kernel(float* __restrict__ dst, const float* __restrict__ table, const int64_t* __restrict__ tok, const int32_t* __restrict__ last, int64_t n,
+                                          int cols, int64_t mul_prev, int64_t mul_cur, int64_t buckets) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int64_t t = i / cols;
+    const int c = (int)(i - t * cols);
+    const int64_t prev = t > 0 ? tok[t - 1] : (int64_t)last[0] - 1;
+    const int64_t row = prev < 0 ? buckets : (prev * mul_prev + tok[t] * mul_cur) % buckets;
+    dst[i] += table[row * cols + c];
+}
+__global__ void pair_hash_last_kernel(const int64_t* __restrict__ tok, int32_t* __restrict__ last, int n) { last[0] = (int32_t)tok[n - 1] + 1; }
+extern "C" CC_API int cc_pair_hash_rows_add(cc_device* dev, const cc_view* dst, const cc_view* table, const int64_t* tokens, int32_t n, int32_t slot, const cc_view* last,
+                                            int64_t mul_prev, int64_t mul_cur, int64_t buckets) {
+    SEQ_ENTER(dev, "pair_hash_rows_add");
+    SEQ_F32(dev, dst, "pair_hash_rows_add dst"); SEQ_F32(dev, table, "pair_hash_rows_add table");
+    SEQ_VIEW(dev, last, "pair_hash_rows_add last");
+    CC_REQUIRE(dev, last->buf->dtype == CC_I32 && view_len(last) == 1, "pair_hash_rows_add: last must be I32 [1]");
+    CC_REQUIRE(dev, dst->ndim == 2 && table->ndim == 2 && dst->shape[1] == table->shape[1] && buckets >= 1 && table->shape[0] == buckets + 1 && mul_prev >= 0 && mul_cur >= 0,
+               "pair_hash_rows_add: dst must be [n, cols] and table [buckets + 1, cols]");
+    CC_REQUIRE(dev, n >= 0 && dst->shape[0] == n && (tokens || (n == 1 && slot >= 0 && slot < CC_N_SLOTS)), "pair_hash_rows_add: %d tokens for %lld rows", n, (long long)dst->shape[0]);
+    if (n == 0) return CC_OK;
+    const int64_t* tok = nullptr;
+    if (tokens) {
+        for (int i = 0; i < n; i++) CC_REQUIRE(dev, tokens[i] >= 0 && tokens[i] < ((int64_t)1 << 31) - 1, "pair_hash_rows_add: token id %lld", (long long)tokens[i]);
+        int rc = cc_ensure_dev_idx(dev, (size_t)n * 8);
+        if (rc) return rc;
+        CC_CUDA(dev, cudaMemcpyAsync(dev->dev_idx, tokens, (size_t)n * 8, cudaMemcpyHostToDevice, dev->stream));
+        tok = (const int64_t*)dev->dev_idx;
+    } else {
+        int rc = cc_ensure_slots(dev);
+        if (rc) return rc;
+        tok = dev->slots + slot;
+    }
+    const int64_t total = (int64_t)n * dst->shape[1];
+    int32_t* lp = (int32_t*)last->buf->plane[0];
+    pair_hash_rows_add_kernel<<<(unsigned)((total + 255) / 256), 256, 0, dev->stream>>>(fptr(dst), fptr(table), tok, lp, total, (int)dst->shape[1], mul_prev, mul_cur, buckets);
+    dev->launches++;
+    pair_hash_last_kernel<<<1, 1, 0, dev->stream>>>(tok, lp, n);
+    CC_LAUNCH_CHECK(dev);
+    return CC_OK;
+}
 
 // ---- short causal convolution ----------------------------------------------------------------------------------------------------
 // one warp per (token, run of hs channels).  in[t'] for t' < 0 comes from the tail: tail row (K-1) + t'.
-__global__ void short_conv_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ tail, float* __restrict__ y, int T, int C,
-                                  int K, int hs, int act, int unit, float ueps, float uscale) {
+__global__ void short_conv_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias, const float* __restrict__ tail,
+                                  float* __restrict__ y, int T, int C, int K, int hs, int act, int unit, float ueps, float uscale) {
     const int heads = C / hs;
     const int64_t u = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
@@ -125,7 +248,7 @@ __global__ void short_conv_kernel(const float* __restrict__ x, const float* __re
     float ss = 0.0f;
     for (int cc = lane; cc < hs; cc += 32) {
         const int c = h * hs + cc;
-        float acc = 0.0f;
+        float acc = bias ? bias[c] : 0.0f;
         for (int j = 0; j < K; j++) {
             const int ti = t - (K - 1) + j;
             const float v = ti >= 0 ? x[(int64_t)ti * C + c] : tail[(int64_t)(ti + K - 1) * C + c];
@@ -150,8 +273,8 @@ __global__ void short_conv_tail_kernel(const float* __restrict__ x, float* __res
         tail[(int64_t)j * C + c] = ti >= 0 ? x[(int64_t)ti * C + c] : tail[(int64_t)(ti + K - 1) * C + c];
     }
 }
-extern "C" CC_API int cc_short_conv(cc_device* dev, const cc_view* x, const cc_view* w, const cc_view* tail, int32_t act, int32_t head_size, int32_t unit_norm,
-                                    float unit_eps, float unit_scale, cc_buf** out) {
+static int short_conv_impl(cc_device* dev, const cc_view* x, const cc_view* w, const cc_view* bias, const cc_view* tail, int32_t act, int32_t head_size, int32_t unit_norm,
+                           float unit_eps, float unit_scale, cc_buf** out) {
     SEQ_ENTER(dev, "short_conv");
     if (!out) return cc_fail(dev, CC_ERR_ARG, "short_conv: out is NULL");
     SEQ_F32(dev, x, "short_conv x"); SEQ_F32(dev, w, "short_conv w");
@@ -164,6 +287,7 @@ extern "C" CC_API int cc_short_conv(cc_device* dev, const cc_view* x, const cc_v
     }
     const int hs = head_size > 0 ? head_size : (int)C;
     CC_REQUIRE(dev, C % hs == 0, "short_conv: head_size %d does not divide %lld channels", hs, (long long)C);
+    if (bias) { SEQ_F32(dev, bias, "short_conv bias"); CC_REQUIRE(dev, view_len(bias) == C, "short_conv: the bias needs one number per channel"); }
     cc_buf* y = nullptr;
     int rc = cc_new_activation(dev, T * C, CC_F32, false, &y);
     if (rc) return rc;
@@ -171,13 +295,22 @@ extern "C" CC_API int cc_short_conv(cc_device* dev, const cc_view* x, const cc_v
     if (T == 0) return CC_OK;
     const float* tp = K > 1 ? fptr(tail) : nullptr;
     const int64_t units = T * (C / hs);
-    short_conv_kernel<<<(unsigned)((units + 7) / 8), 256, 0, dev->stream>>>(fptr(x), fptr(w), tp, (float*)y->base, (int)T, (int)C, (int)K, hs, act, unit_norm, unit_eps, unit_scale);
+    short_conv_kernel<<<(unsigned)((units + 7) / 8), 256, 0, dev->stream>>>(fptr(x), fptr(w), bias ? fptr(bias) : nullptr, tp, (float*)y->base, (int)T, (int)C, (int)K, hs, act, unit_norm,
+                                                                        unit_eps, unit_scale);
     CC_LAUNCH_CHECK(dev);
     if (K > 1) {
         short_conv_tail_kernel<<<(unsigned)((C + 127) / 128), 128, 0, dev->stream>>>(fptr(x), fptr(tail), (int)T, (int)C, (int)K);
         CC_LAUNCH_CHECK(dev);
     }
     return CC_OK;
+}
+
+extern "C" CC_API int cc_short_conv(cc_device* dev, const cc_view* x, const cc_view* w, const cc_view* tail, int32_t act, int32_t head_size, int32_t unit_norm,
+                                    float unit_eps, float unit_scale, cc_buf** out) {
+    return short_conv_impl(dev, x, w, nullptr, tail, act, head_size, unit_norm, unit_eps, unit_scale, out);
+}
+extern "C" CC_API int cc_short_conv_bias(cc_device* dev, const cc_view* x, const cc_view* w, const cc_view* bias, const cc_view* tail, int32_t act, cc_buf** out) {
+    return short_conv_impl(dev, x, w, bias, tail, act, 0, 0, 0.0f, 1.0f, out);
 }
 
 // ---- gated delta rule -------------------------------------------------------------------------------------------------------------
@@ -430,11 +563,15 @@ extern "C" CC_API int cc_kv_ring_append(cc_device* dev, const cc_view* kring, co
 #define WA_K 16
 #define WA_THREADS 256
 struct WaGeom {
-    int T, H, G, R, dk, dv, window, ring, QT, cap;      // QT queries per tile; cap = row stride of S
+    int T, H, G, R, dk, dv, window, block, ring, QT, cap;      // QT queries per tile; cap = row stride of S; block > 0: a query sees only its own block of positions
     int krs, vrs, vhs;                                  // floats between two rows of the key / value ring (vhs: between two heads' values inside a row)
     int64_t pos0;
 };
-__device__ __forceinline__ int64_t wa_lo(const WaGeom& g, int64_t i) { return (g.window > 0 && i - g.window + 1 > 0) ? i - g.window + 1 : 0; }
+__host__ __device__ __forceinline__ int64_t wa_lo(const WaGeom& g, int64_t i) {
+    int64_t lo = (g.window > 0 && i - g.window + 1 > 0) ? i - g.window + 1 : 0;
+    if (g.block > 0) { const int64_t b = i - i % g.block; lo = b > lo ? b : lo; }
+    return lo;
+}
 
 __global__ void head_rms_norm_kernel(float* __restrict__ x, const float* __restrict__ w, int64_t n_units, int hs, float eps) {
     const int64_t u = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -757,9 +894,8 @@ __global__ void __launch_bounds__(WA_THREADS) wa_values_kernel(const float* __re
         }
     }
 }
-extern "C" CC_API int cc_window_attention_sink(cc_device* dev, const cc_view* q, const cc_view* qnw, float eps, const cc_view* kring, const cc_view* vring, int64_t pos0,
-                                               int32_t H, int32_t G, int32_t dk, int32_t dv, int32_t window, float scale, const cc_view* r1, const cc_view* r2,
-                                               const cc_view* sink, cc_buf** out) {
+static int masked_attention_impl(cc_device* dev, const cc_view* q, const cc_view* qnw, float eps, const cc_view* kring, const cc_view* vring, int64_t pos0, int32_t H, int32_t G,
+                                 int32_t dk, int32_t dv, int32_t window, int32_t block, float scale, const cc_view* r1, const cc_view* r2, const cc_view* sink, cc_buf** out) {
     SEQ_ENTER(dev, "window_attention");
     if (!out) return cc_fail(dev, CC_ERR_ARG, "window_attention: out is NULL");
     SEQ_F32(dev, q, "window_attention q"); SEQ_F32(dev, kring, "window_attention kring");
@@ -778,19 +914,24 @@ extern "C" CC_API int cc_window_attention_sink(cc_device* dev, const cc_view* q,
     const float* vptr = vring ? fptr(vring) : fptr(kring);            // no value ring: a key row's first dv columns are its value
     // the oldest row the first query needs must not have been overwritten by the newest row of this call
     const int64_t last = pos0 + T - 1;
-    const int64_t oldest = window > 0 ? (pos0 - window + 1 > 0 ? pos0 - window + 1 : 0) : 0;
-    CC_REQUIRE(dev, T == 0 || last - oldest + 1 <= ring, "window_attention: positions %lld..%lld with window %d need more than the ring's %lld rows",
-               (long long)pos0, (long long)last, window, (long long)ring);
+    WaGeom g;
+    g.window = window; g.block = block;
+    const int64_t oldest = wa_lo(g, pos0);
+    CC_REQUIRE(dev, T == 0 || last - oldest + 1 <= ring, "window_attention: positions %lld..%lld with window %d, block %d need more than the ring's %lld rows",
+               (long long)pos0, (long long)last, window, block, (long long)ring);
     cc_buf* o = nullptr;
     int rc = cc_new_activation(dev, T * H * dv, CC_F32, false, &o);
     if (rc) return rc;
     *out = o;
     if (T == 0) return CC_OK;
-    const int64_t maxn = window > 0 ? (window < last + 1 ? window : last + 1) : last + 1;
+    // the most keys one query can see
+    int64_t reach = last + 1;
+    if (window > 0 && window < reach) reach = window;
+    if (block > 0 && block < reach) reach = block;
+    const int64_t maxn = reach;
     const int R = H / G;
     CC_REQUIRE(dev, R <= WA_TILE, "window_attention: %d query heads per key/value head (at most %d)", R, WA_TILE);
-    WaGeom g;
-    g.T = (int)T; g.H = H; g.G = G; g.R = R; g.dk = dk; g.dv = dv; g.window = window; g.ring = (int)ring; g.QT = WA_TILE / R; g.cap = (int)maxn; g.pos0 = pos0;
+    g.T = (int)T; g.H = H; g.G = G; g.R = R; g.dk = dk; g.dv = dv; g.ring = (int)ring; g.QT = WA_TILE / R; g.cap = (int)maxn; g.pos0 = pos0;
     g.krs = G * dk; g.vrs = vring ? G * dv : G * dk; g.vhs = vring ? dv : dk;
     float* qp = fptr(q);
     if (qnw) {             // the query norm, in place: q is this call's private projection output in every caller of the runner; a caller that
@@ -802,7 +943,7 @@ extern "C" CC_API int cc_window_attention_sink(cc_device* dev, const cc_view* q,
     rc = cc_pool_alloc(dev, (size_t)T * H * maxn * 4, &Sp, &cls);
     if (rc) return rc;
     const int q_tiles = (int)((T + g.QT - 1) / g.QT);
-    const int64_t band = window > 0 ? (int64_t)window - 1 + g.QT : last + 1;          // keys a query tile can see
+    const int64_t band = reach - 1 + g.QT;                                             // keys a query tile can see
     const int64_t band_max = band < last + 1 ? band : last + 1;
     const bool few_rows = T * H <= 64;
     if (few_rows && (size_t)R * dk * 4 <= 160 * 1024) {
@@ -841,6 +982,15 @@ extern "C" CC_API int cc_window_attention_sink(cc_device* dev, const cc_view* q,
     CC_LAUNCH_CHECK(dev);
     return CC_OK;
 }
+extern "C" CC_API int cc_window_attention_sink(cc_device* dev, const cc_view* q, const cc_view* qnw, float eps, const cc_view* kring, const cc_view* vring, int64_t pos0,
+                                               int32_t H, int32_t G, int32_t dk, int32_t dv, int32_t window, float scale, const cc_view* r1, const cc_view* r2,
+                                               const cc_view* sink, cc_buf** out) {
+    return masked_attention_impl(dev, q, qnw, eps, kring, vring, pos0, H, G, dk, dv, window, 0, scale, r1, r2, sink, out);
+}
+extern "C" CC_API int cc_masked_attention(cc_device* dev, const cc_view* q, const cc_view* kring, const cc_view* vring, int64_t pos0, int32_t H, int32_t G, int32_t dk, int32_t dv,
+                                          int32_t window, int32_t block, float scale, const cc_view* sink, cc_buf** out) {
+    return masked_attention_impl(dev, q, nullptr, 0.0f, kring, vring, pos0, H, G, dk, dv, window, block, scale, nullptr, nullptr, sink, out);
+}
 extern "C" CC_API int cc_window_attention(cc_device* dev, const cc_view* q, const cc_view* qnw, float eps, const cc_view* kring, const cc_view* vring, int64_t pos0,
                                           int32_t H, int32_t G, int32_t dk, int32_t dv, int32_t window, float scale, const cc_view* r1, const cc_view* r2,
                                           cc_buf** out) {
@@ -872,6 +1022,38 @@ extern "C" CC_API int cc_group_rms_norm(cc_device* dev, const cc_view* dst, cons
     if (rows == 0) return CC_OK;
     const int64_t units = rows * groups;
     group_rms_norm_kernel<<<(unsigned)((units + 7) / 8), 256, 0, dev->stream>>>(fptr(dst), fptr(x), fptr(w), units, groups, (int)(cols / groups), eps);
+    CC_LAUNCH_CHECK(dev);
+    return CC_OK;
+}
+
+// the gate first, then the norm: one warp per (row, group)
+__global__ void gated_group_rms_norm_kernel(float* __restrict__ dst, const float* __restrict__ x, const float* __restrict__ gate, const float* __restrict__ w, int64_t n_units,
+                                            int groups, int gs, float eps, int act) {
+    const int64_t u = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (u >= n_units) return;
+    const float* xr = x + u * gs;
+    const float* gr = gate + u * gs;
+    const float* wr = w + (u % groups) * gs;
+    float ss = 0.0f;
+    for (int c = lane; c < gs; c += 32) { const float v = xr[c] * seq_act(gr[c], act); ss = fmaf(v, v, ss); }
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)gs + eps);
+    float* dr = dst + u * gs;
+    for (int c = lane; c < gs; c += 32) dr[c] = xr[c] * seq_act(gr[c], act) * inv * wr[c];
+}
+extern "C" CC_API int cc_gated_group_rms_norm(cc_device* dev, const cc_view* dst, const cc_view* x, const cc_view* gate, const cc_view* w, int32_t groups, float eps,
+                                              int32_t gate_act) {
+    SEQ_ENTER(dev, "gated_group_rms_norm");
+    SEQ_F32(dev, dst, "gated_group_rms_norm dst"); SEQ_F32(dev, x, "gated_group_rms_norm x"); SEQ_F32(dev, gate, "gated_group_rms_norm gate"); SEQ_F32(dev, w, "gated_group_rms_norm w");
+    CC_REQUIRE(dev, x->ndim == 2 && dst->ndim == 2 && dst->shape[0] == x->shape[0] && dst->shape[1] == x->shape[1] && view_len(gate) == view_len(x),
+               "gated_group_rms_norm: dst, x and gate must be [rows, cols]");
+    const int64_t rows = x->shape[0], cols = x->shape[1];
+    CC_REQUIRE(dev, groups >= 1 && cols % groups == 0 && view_len(w) == cols, "gated_group_rms_norm: %lld columns, %d groups, %lld weights", (long long)cols, groups,
+               (long long)view_len(w));
+    if (rows == 0) return CC_OK;
+    const int64_t units = rows * groups;
+    gated_group_rms_norm_kernel<<<(unsigned)((units + 7) / 8), 256, 0, dev->stream>>>(fptr(dst), fptr(x), fptr(gate), fptr(w), units, groups, (int)(cols / groups), eps, gate_act);
     CC_LAUNCH_CHECK(dev);
     return CC_OK;
 }
@@ -1047,7 +1229,7 @@ extern "C" CC_API int cc_head_concat_shared(cc_device* dev, const cc_view* a, co
 }
 
 // ---- column blocks of one product's result as separate tensors ------------------------------------------------------------------------------
-#define SPLIT_MAX 8
+#define SPLIT_MAX 16
 struct SplitArgs {
     float* dst[SPLIT_MAX];
     int end[SPLIT_MAX];          // first column behind part p

@@ -54,3 +54,11 @@ def _load_meresun(path, device, dtype="bfloat16", chunk=0, max_tokens=0, **_):
 
 
 register("Meresun", _load_meresun)
+
+
+def _load_vuzinex(path, device, dtype="bfloat16", chunk=0, max_tokens=0, **_):
+    from . import vuzinex
+    return vuzinex.load(path, device, dtype, chunk, max_tokens)
+
+
+register("Vuzinex", _load_vuzinex)

@@ -27,9 +27,26 @@ def yarn_table(dims: int, base: float, factor: float, original: float, fast: flo
     return f / factor * ramp + f * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
 
 
+def wavelength_band_table(dims: int, base: float, factor: float, original: float, low: float, high: float):
+    """Scaling by wavelength bands (the Llama 3.1 rule): a pair whose wavelength is shorter than original / high keeps its frequency, one
+    whose wavelength is longer than original / low has it divided by `factor`, and between the two the frequency is the blend
+    (1 - s) f / factor + s f with s = (original / wavelength - low) / (high - low)."""
+    f, _ = plain_table(dims, base)
+    wave = 2.0 * math.pi / f
+    s = (original / wave - low) / (high - low)
+    blend = (1.0 - s) * f / factor + s * f
+    return np.where(wave < original / high, f, np.where(wave > original / low, f / factor, blend)), 1.0
+
+
 def table_of(rot: dict):
-    """rot: {"dims", "base", optional "scaling": {"factor", "original", "fast", "slow"}} -> (float32 frequencies [dims / 2], factor)"""
+    """rot: {"dims", "base", optional "scaling"} -> (float32 frequencies [dims / 2], factor on cos and sin).  The scaling's keys say which
+    rule it is: {"factor", "original", "fast", "slow"} is YaRN, {"factor", "original", "low", "high"} the wavelength bands."""
     dims, base = int(rot["dims"]), float(rot["base"])
     sc = rot.get("scaling")
-    f, mag = yarn_table(dims, base, float(sc["factor"]), float(sc["original"]), float(sc["fast"]), float(sc["slow"])) if sc else plain_table(dims, base)
+    if not sc:
+        f, mag = plain_table(dims, base)
+    elif "low" in sc or "high" in sc:
+        f, mag = wavelength_band_table(dims, base, float(sc["factor"]), float(sc["original"]), float(sc["low"]), float(sc["high"]))
+    else:
+        f, mag = yarn_table(dims, base, float(sc["factor"]), float(sc["original"]), float(sc["fast"]), float(sc["slow"]))
     return f.astype(np.float32), float(mag)

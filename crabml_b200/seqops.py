@@ -144,3 +144,78 @@ def moe_experts_glu(x, ids, weights, w_gate, w_up, w_down, n_experts, ff, act=ca
     x.device.check(x.device.lib.cc_moe_experts_glu(x.device.handle, _v(x), _v(ids), _v(weights), _v(w_gate), _v(w_up), _v(w_down), int(n_experts), int(ff), C.byref(gp),
                                                    C.byref(h)))
     return _new(x.device, h, list(x.shape()))
+
+
+def rms_norm_gain_mult(dst, y, gain, eps, mult):
+    dst.device.check(dst.device.lib.cc_rms_norm_gain_mult(dst.device.handle, _v(dst), _v(y), _v(gain), float(eps), float(mult)))
+    return dst
+
+
+def head_rms_norm(x, w, head_size, eps, gate=None, gate_act=capi.ACT_NONE):
+    """cc_gated_head_rms_norm with its optional operands: w None (no weight), [head_size] or one per column; gate None (no gate)"""
+    x.device.check(x.device.lib.cc_gated_head_rms_norm(x.device.handle, _v(x), _v(gate), _v(w), int(head_size), float(eps), int(gate_act)))
+    return x
+
+
+def gated_group_rms_norm(x, gate, w, groups, eps, gate_act=capi.ACT_SILU, dst=None):
+    dst = dst if dst is not None else type(x).alloc(x.shape(), capi.F32, x.device)
+    x.device.check(x.device.lib.cc_gated_group_rms_norm(x.device.handle, _v(dst), _v(x), _v(gate), _v(w), int(groups), float(eps), int(gate_act)))
+    return dst
+
+
+def glu_halves(src, bias=None, act=capi.ACT_SILU):
+    h = C.c_void_p()
+    src.device.check(src.device.lib.cc_glu_halves(src.device.handle, _v(src), _v(bias), int(act), C.byref(h)))
+    return _new(src.device, h, [src.shape()[0], src.shape()[1] // 2])
+
+
+def add_row_bias(x, bias):
+    x.device.check(x.device.lib.cc_add_row_bias(x.device.handle, _v(x), _v(bias)))
+    return x
+
+
+def scaled_sum(dst, a, sa, b, sb):
+    dst.device.check(dst.device.lib.cc_scaled_sum(dst.device.handle, _v(dst), _v(a), float(sa), _v(b), float(sb)))
+    return dst
+
+
+def pair_hash_rows_add(dst, table, tokens, last, mul_prev, mul_cur, buckets, slot=-1):
+    """tokens: a list of ids, or None to take ONE id from device slot `slot`; last: I32 [1] state"""
+    n = len(tokens) if tokens is not None else 1
+    arr = (C.c_int64 * n)(*[int(t) for t in tokens]) if tokens is not None else None
+    dst.device.check(dst.device.lib.cc_pair_hash_rows_add(dst.device.handle, _v(dst), _v(table), arr, n, int(slot), _v(last), int(mul_prev), int(mul_cur), int(buckets)))
+    return dst
+
+
+def short_conv_bias(x, w, bias, tail, act=capi.ACT_SILU):
+    h = C.c_void_p()
+    x.device.check(x.device.lib.cc_short_conv_bias(x.device.handle, _v(x), _v(w), _v(bias), _v(tail), int(act), C.byref(h)))
+    return _new(x.device, h, x.shape())
+
+
+def masked_attention(q, kring, vring, pos0, n_heads, n_kv, dk, dv, scale, window=0, block=0, sink=None):
+    h = C.c_void_p()
+    q.device.check(q.device.lib.cc_masked_attention(q.device.handle, _v(q), _v(kring), _v(vring), int(pos0), n_heads, n_kv, dk, dv, int(window), int(block), float(scale),
+                                                    _v(sink), C.byref(h)))
+    return _new(q.device, h, [q.shape()[0], n_heads * dv])
+
+
+def matrix_memory(q, k, v, gi, gf, bi, bf, cap, q_scale, state, mstate, n_heads, dk, dv):
+    h = C.c_void_p()
+    q.device.check(q.device.lib.cc_matrix_memory(q.device.handle, _v(q), _v(k), _v(v), _v(gi), _v(gf), _v(bi), _v(bf), float(cap), float(q_scale), _v(state), _v(mstate),
+                                                 n_heads, dk, dv, C.byref(h)))
+    return _new(q.device, h, [q.shape()[0], n_heads * dv])
+
+
+def decayed_linear_attention(q, k, v, z, zb, tau, q_scale, state, n_heads, dk, dv):
+    h = C.c_void_p()
+    q.device.check(q.device.lib.cc_decayed_linear_attention(q.device.handle, _v(q), _v(k), _v(v), _v(z), _v(zb), float(tau), float(q_scale), _v(state), n_heads, dk, dv,
+                                                            C.byref(h)))
+    return _new(q.device, h, [q.shape()[0], n_heads * dv])
+
+
+def state_space_scan(xbc, dt, dt_bias, a_log, d_skip, state, n_heads, n_groups, n_state, head_dim):
+    h = C.c_void_p()
+    xbc.device.check(xbc.device.lib.cc_state_space_scan(xbc.device.handle, _v(xbc), _v(dt), _v(dt_bias), _v(a_log), _v(d_skip), _v(state), n_heads, n_groups, n_state,
+                                                        head_dim, C.byref(h)))
+    return _new(xbc.device, h, [xbc.shape()[0], n_heads * head_dim])

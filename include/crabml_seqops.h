@@ -22,7 +22,7 @@ extern "C" {
 #endif
 
 /* CC_ACT_SWISH: z * sigmoid(alpha * z) with alpha given beside it (cc_glu_params); the others take no constant */
-enum cc_activation { CC_ACT_NONE = 0, CC_ACT_SILU = 1, CC_ACT_GELU_TANH = 2, CC_ACT_SWISH = 3 };
+enum cc_activation { CC_ACT_NONE = 0, CC_ACT_SILU = 1, CC_ACT_GELU_TANH = 2, CC_ACT_SWISH = 3, CC_ACT_SIGMOID = 4 };
 
 /* x (any shape) = 0 */
 CC_API int cc_tensor_zero(cc_device* dev, const cc_view* x);
@@ -31,12 +31,21 @@ CC_API int cc_tensor_zero(cc_device* dev, const cc_view* x);
 /* dst[r] = (accumulate ? dst[r] : 0) + y[r] / sqrt(mean(y[r]^2) + eps) * gain ; dst, y: [rows, cols]; gain: 1 element (one number
  * for all coordinates) or cols elements.  accumulate = 1 is the residual update of a block whose norm sits on the sublayer OUTPUT. */
 CC_API int cc_rms_norm_gain(cc_device* dev, const cc_view* dst, const cc_view* y, const cc_view* gain, float eps, int32_t accumulate);
-/* x[r, h, :] = x[r, h, :] / sqrt(mean(x[r, h, :]^2) + eps) * w[:] * act(gate[r, h, :]) ; x, gate: [rows, heads * head_size], w: [head_size] */
+/* dst[r] = dst[r] + mult * (y[r] / sqrt(mean(y[r]^2) + eps) * gain): cc_rms_norm_gain with accumulate = 1 and a factor on the normed
+ * sublayer output (a residual multiplier), applied after the gain. */
+CC_API int cc_rms_norm_gain_mult(cc_device* dev, const cc_view* dst, const cc_view* y, const cc_view* gain, float eps, float mult);
+/* x[r, h, :] = x[r, h, :] / sqrt(mean(x[r, h, :]^2) + eps) * w * act(gate[r, h, :]) ; x, gate: [rows, heads * head_size].  w: [head_size]
+ * (one weight vector for all heads) or [heads * head_size] (a weight per column; x must then be 2-D) or NULL (1).  gate NULL: no gate
+ * (the plain per-head norm of queries and keys). */
 CC_API int cc_gated_head_rms_norm(cc_device* dev, const cc_view* x, const cc_view* gate, const cc_view* w, int32_t head_size, float eps,
                                   int32_t gate_act);
 /* dst[r] = x[r] with every one of `groups` equal consecutive parts of the row divided by its own sqrt(mean(part^2) + eps), times w[:]
  * (w: cols numbers).  groups = 1 is the plain weighted RMS norm.  dst may be x. */
 CC_API int cc_group_rms_norm(cc_device* dev, const cc_view* dst, const cc_view* x, const cc_view* w, int32_t groups, float eps);
+/* dst = x * act(gate) with every one of `groups` equal consecutive parts of the row then divided by its own root mean square, times w[:]:
+ * the gate comes BEFORE the norm (cc_gated_head_rms_norm gates after it).  All [rows, cols]; w: [cols].  dst may be x. */
+CC_API int cc_gated_group_rms_norm(cc_device* dev, const cc_view* dst, const cc_view* x, const cc_view* gate, const cc_view* w, int32_t groups, float eps,
+                                   int32_t gate_act);
 /* PolyNorm, in place on z [rows, cols]: z <- a N(z) + b N(z^2) + c N(z^3) + e with coef = {a, b, c, e}; powers are taken element by
  * element and N divides the row by its root mean square, N(y) = y / sqrt(mean(y^2) + eps). */
 CC_API int cc_poly_norm(cc_device* dev, const cc_view* z, const cc_view* coef, float eps);
@@ -44,12 +53,27 @@ CC_API int cc_poly_norm(cc_device* dev, const cc_view* z, const cc_view* coef, f
  * that operand is not gated; y2 NULL: one operand.  The residual update of a block whose sublayers run side by side on one input. */
 CC_API int cc_gated_sum(cc_device* dev, const cc_view* dst, int32_t accumulate, const cc_view* y1, const cc_view* g1, const cc_view* b1, const cc_view* y2,
                         const cc_view* g2, const cc_view* b2);
-/* src [rows, cols] cut into n_parts (<= 8) blocks of neighbouring columns, widths[p] wide, each returned as a contiguous tensor
+/* src [rows, cols] cut into n_parts (<= 16) blocks of neighbouring columns, widths[p] wide, each returned as a contiguous tensor
  * [rows, widths[p]] in outs[p].  For matrices that multiply the same input and are stacked one under the other: ONE product (one launch,
  * one conversion of the input), then this. */
 CC_API int cc_split_cols(cc_device* dev, const cc_view* src, int32_t n_parts, const int32_t* widths, cc_buf** outs);
 /* gate = act(gate) * up, elementwise (the inner step of a gated feed-forward, exact 32-bit activation) */
 CC_API int cc_glu_inplace(cc_device* dev, const cc_view* gate, const cc_view* up, int32_t act);
+/* The same step on ONE product of the stacked matrix [W_gate ; W_up]: src [rows, 2 * ff] holds gate | up side by side;
+ * out[r, c] = act(src[r, c] + bias[c]) * (src[r, ff + c] + bias[ff + c]) ; bias: [2 * ff] or NULL.  out: [rows, ff]. */
+CC_API int cc_glu_halves(cc_device* dev, const cc_view* src, const cc_view* bias, int32_t act, cc_buf** out);
+/* x[r, c] += bias[c] ; x: [rows, cols], bias: [cols] (the bias of a projection, added to its product) */
+CC_API int cc_add_row_bias(cc_device* dev, const cc_view* x, const cc_view* bias);
+/* dst = sa * a + sb * b, elementwise (two branches that read one input, joined with fixed weights); dst may be a or b */
+CC_API int cc_scaled_sum(cc_device* dev, const cc_view* dst, const cc_view* a, float sa, const cc_view* b, float sb);
+
+/* ---- a second embedding row chosen by a hash of the token pair ------------------------------------------------------------------ */
+/* dst[t] += table[row_t], row_t = (prev_t * mul_prev + token_t * mul_cur) mod buckets, where prev_t is the token before token_t in the
+ * sequence; a sequence's first token takes row `buckets` (table: [buckets + 1, cols]).  The n tokens come from the host (`tokens`) or,
+ * when tokens is NULL, ONE token from device slot `slot` (cc_argmax_to_slot).  last: I32 [1], part of the sequence's state: 1 + the
+ * sequence's last token so far (0: none yet); read for prev_0, then set to 1 + the last of these tokens. */
+CC_API int cc_pair_hash_rows_add(cc_device* dev, const cc_view* dst, const cc_view* table, const int64_t* tokens, int32_t n, int32_t slot, const cc_view* last,
+                                 int64_t mul_prev, int64_t mul_cur, int64_t buckets);
 
 /* ---- short causal convolution over time (depthwise) --------------------------------------------------------------------------- */
 /* x: [T, C] the new inputs of one sequence; w: [C, K] (the last column multiplies the current input); tail: [K-1, C], the K-1 inputs
@@ -58,6 +82,9 @@ CC_API int cc_glu_inplace(cc_device* dev, const cc_view* gate, const cc_view* up
  * sqrt(sum of its squares + unit_eps) and multiplied by unit_scale. */
 CC_API int cc_short_conv(cc_device* dev, const cc_view* x, const cc_view* w, const cc_view* tail, int32_t act, int32_t head_size,
                          int32_t unit_norm, float unit_eps, float unit_scale, cc_buf** out);
+
+/* cc_short_conv with a bias per channel added to the sum before the activation (bias: [C] or NULL) */
+CC_API int cc_short_conv_bias(cc_device* dev, const cc_view* x, const cc_view* w, const cc_view* bias, const cc_view* tail, int32_t act, cc_buf** out);
 
 /* ---- gated delta rule ------------------------------------------------------------------------------------------------------ */
 /* One sequence, T new tokens.  q, k: [T, n_kv * dk] (already normalised), v: [T, n_heads * dv]; a, b: [T, n_heads] raw projections;
@@ -90,6 +117,36 @@ CC_API int cc_window_attention(cc_device* dev, const cc_view* q, const cc_view* 
 CC_API int cc_window_attention_sink(cc_device* dev, const cc_view* q, const cc_view* q_norm_w, float eps, const cc_view* kring, const cc_view* vring,
                                     int64_t pos0, int32_t n_heads, int32_t n_kv, int32_t dk, int32_t dv, int32_t window, float scale,
                                     const cc_view* r1, const cc_view* r2, const cc_view* sink, cc_buf** out);
+
+/* cc_window_attention_sink with one more kind of mask.  block > 0: positions are cut into blocks of `block` counted from position 0 of the
+ * sequence, and position i sees j <= i only inside its own block, floor(i / block) == floor(j / block).  window and block may both be
+ * given (both limits hold); both <= 0: every j <= i. */
+CC_API int cc_masked_attention(cc_device* dev, const cc_view* q, const cc_view* kring, const cc_view* vring, int64_t pos0, int32_t n_heads, int32_t n_kv, int32_t dk,
+                               int32_t dv, int32_t window, int32_t block, float scale, const cc_view* sink, cc_buf** out);
+
+/* ---- linear recurrences over a matrix state -------------------------------------------------------------------------------------------
+ * Three mixers share one form: per head a state S [dk, dv] (F32, carried between calls, zero at the start of a sequence) that every token
+ * first shrinks and then adds an outer product to, and a read-out S^T q.  They differ in what shrinks S and what scales the outer product;
+ * all of that is computed in 32-bit floats from raw projections, inside the op.  One sequence, T new tokens, in order. */
+/* Matrix memory with exponential gates and a running maximum (the mLSTM of xLSTM).  q, k: [T, H * dk], v: [T, H * dv]; gi, gf: [T, H] raw
+ * gate projections with biases bi, bf [H]; state: [H, dk, dv + 1], the matrix S and, as its last column, the normaliser n; mstate: [H],
+ * the running maximum m, which starts at 0 like the rest.
+ *   i = cap tanh((gi + bi) / cap) ; f = logsigmoid(cap tanh((gf + bf) / cap)) ; m' = max(f + m, i)
+ *   S = exp(f + m - m') S + exp(i - m') k v^T ; n likewise with k alone ; out = S^T (q_scale q) / (max(|n . q_scale q|, exp(-m')) + 1e-6)
+ * out: [T, H * dv]. */
+CC_API int cc_matrix_memory(cc_device* dev, const cc_view* q, const cc_view* k, const cc_view* v, const cc_view* gi, const cc_view* gf, const cc_view* bi,
+                            const cc_view* bf, float cap, float q_scale, const cc_view* state, const cc_view* mstate, int32_t n_heads, int32_t dk, int32_t dv,
+                            cc_buf** out);
+/* Linear attention with a decay per key channel (gated linear attention).  q, k, z: [T, H * dk], v: [T, H * dv]; zb: [H * dk] bias of z.
+ *   alpha = sigmoid(z + zb)^(1 / tau) ; S = diag(alpha) S + k v^T ; out = S^T (q_scale q) */
+CC_API int cc_decayed_linear_attention(cc_device* dev, const cc_view* q, const cc_view* k, const cc_view* v, const cc_view* z, const cc_view* zb, float tau,
+                                       float q_scale, const cc_view* state, int32_t n_heads, int32_t dk, int32_t dv, cc_buf** out);
+/* Selective state-space recurrence (the SSD form of Mamba-2).  xbc: [T, H * P + 2 * G * N], a row is x | B | C (the convolution's output);
+ * dt: [T, H] raw; dt_bias, a_log, d_skip: [H]; state: [H, N, P].  Head h reads B and C of group h / (H / G).
+ *   d = softplus(dt + dt_bias) ; S = exp(-exp(a_log) d) S + d B x^T ; out = S^T C + d_skip x
+ * out: [T, H * P]. */
+CC_API int cc_state_space_scan(cc_device* dev, const cc_view* xbc, const cc_view* dt, const cc_view* dt_bias, const cc_view* a_log, const cc_view* d_skip,
+                               const cc_view* state, int32_t n_heads, int32_t n_groups, int32_t n_state, int32_t head_dim, cc_buf** out);
 
 /* ---- rotary positions from a frequency table ----------------------------------------------------------------------------------- */
 /* x: [T, n_heads * head_size], rows are positions pos0 .. ; freq: [P] one frequency per pair.  In every head the columns
