@@ -85,12 +85,15 @@ def rotate(x, rot, pos0=0):
 
 
 # ---- softmax attention ----------------------------------------------------------------------------------------------------------------------
-def visible(T, block):
-    """[T, T] booleans: j <= i, and with block > 0 only inside i's block of `block` positions counted from position 0"""
+def visible(T, block, window=0):
+    """[T, T] booleans: j <= i; with block > 0 only inside i's block of `block` positions counted from position 0; with window > 0 only
+    the last `window` positions, i itself included"""
     i, j = np.arange(T)[:, None], np.arange(T)[None, :]
     ok = j <= i
     if block and block > 0:
         ok &= (i // block) == (j // block)
+    if window and window > 0:
+        ok &= (i - j) < window
     return ok
 
 
@@ -108,7 +111,7 @@ def attention(h, m, w, p, eps):
         q = unit_rms(q, eps) * w[p + "q.norm"]
         k = unit_rms(k, eps) * w[p + "k.norm"]
     q, k = rotate(q, m.get("rot")), rotate(k, m.get("rot"))
-    ok = visible(T, (m.get("mask") or {}).get("size", 0))
+    ok = visible(T, (m.get("mask") or {}).get("size", 0), (m.get("mask") or {}).get("window", 0))
     out = np.zeros((T, H, dv))
     for hd in range(H):
         g = hd // (H // G)
