@@ -42,6 +42,9 @@ WORKLOADS = {
     # the Meresun family at the same layer sizes, beside the Zatorax stack of equal width and depth; see run_meresun
     "meresun-w1024": ("MERESUN", "BF16", "BF16"),
     "meresun-w2048": ("MERESUN", "BF16", "BF16"),
+    # the Vuzinex family at the same layer sizes, beside the Zatorax stack of equal width and depth; see run_vuzinex
+    "vuzinex-w1024": ("VUZINEX", "BF16", "BF16"),
+    "vuzinex-w2048": ("VUZINEX", "BF16", "BF16"),
 }
 # dram bytes per megakernel launch from the committed ncu --set full capture (profiles/); None until captured
 TRAFFIC = {("llama2-7b-q8_0", 1): 7040893000 + 49879296}     # profiles/r02p_mega_ring_q8_0_ncu_raw.csv (mega_ring_kernel: dram__bytes_read.sum + dram__bytes_write.sum)
@@ -621,6 +624,98 @@ def run_meresun(args, rank, world, local_rank):
     print(json.dumps(line))
 
 
+def vuzinex_bench_config(width: int, vocab: int = 32000):
+    """four layers, each run once, each with a dense feed-forward of 3 x width, so that depth and active feed-forward width equal the
+    Zatorax stack's: attention in blocks of 1024 positions with a sink beside the matrix memory; causal attention with biases, norms and a
+    gate beside the decayed linear attention; two state-space layers.  128-wide attention heads, 4 query heads per key head."""
+    H = width // 128
+    G = max(1, H // 4)
+    rot = {"dims": 128, "base": 500000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+    rot2 = {"dims": 64, "base": 10000.0, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    mlp = {"kind": "dense", "ff": 3 * width}
+    a = {"type": "parallel", "mlp": mlp, "mixer": {"left": {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "rot": rot, "mask": {"size": 1024}},
+                                                   "right": {"heads": max(1, H // 2), "dim": 128, "vdim": 128, "gate_cap": 20.0}, "left_scale": 1.0, "right_scale": 1.0}}
+    b = {"type": "parallel_2", "mlp": mlp, "mixer": {"left": {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "rot": rot2},
+                                                     "right": {"heads": max(1, H // 2), "dim": 64, "vdim": 128, "tau": 8.0}, "left_scale": 1.0, "right_scale": 1.0}}
+    c = {"type": "mamba2", "mlp": mlp, "mixer": {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}}
+    return {"architecture": "Vuzinex", "vocab": vocab, "width": width, "embedding": {"scale": 1.0, "bigram": {"buckets": 65536, "mul_prev": 1000003, "mul_cur": 31}},
+            "norm": {"eps": 1e-6}, "residual_mult": 1.0, "logit_scale": 1.0, "layers": [a, b, c, c]}
+
+
+def time_recurrences(dev, width, T):
+    """The recurrence kernels alone at the bench's sizes, beside the closest model's (the gated delta rule): device time of one call over T
+    tokens, and the rate at which state elements are updated (token x head x dk x dv per second)."""
+    from crabml_b200 import CudaTensor, capi, seqops
+    rng = np.random.default_rng(SEED)
+
+    def rand(*shape, scale=1.0):
+        return CudaTensor.new((rng.standard_normal(shape) * scale).astype(np.float32), list(shape), dev)
+
+    def zeros(*shape):
+        return CudaTensor.alloc(list(shape), capi.F32, dev)
+    H = max(1, width // 256)
+    out = {}
+
+    def timed(name, heads, dk, dv, f):
+        f()
+        dev.synchronize(); dev.timer_begin()
+        for _ in range(3):
+            f()
+        ms = dev.timer_end() / 3
+        out[name] = {"heads": heads, "dk": dk, "dv": dv, "tokens": T, "ms": ms, "state_updates_per_s": T * heads * dk * dv / (ms * 1e-3)}
+    q, k, v = rand(T, H * 128, scale=0.1), rand(T, H * 128, scale=0.1), rand(T, H * 128)
+    gi, gf, bz = rand(T, H), rand(T, H), zeros(H)
+    S, ms_ = zeros(H, 128, 129), zeros(H)
+    timed("matrix_memory", H, 128, 128, lambda: seqops.matrix_memory(q, k, v, gi, gf, bz, bz, 20.0, 128 ** -0.5, S, ms_, H, 128, 128))
+    q2, k2, z2, zb = rand(T, H * 64, scale=0.1), rand(T, H * 64, scale=0.1), rand(T, H * 64), zeros(H * 64)
+    S2 = zeros(H, 64, 128)
+    timed("decayed_linear_attention", H, 64, 128, lambda: seqops.decayed_linear_attention(q2, k2, v, z2, zb, 8.0, 0.125, S2, H, 64, 128))
+    Hs = 2 * width // 64
+    xbc, dt, hb = rand(T, Hs * 64 + 256, scale=0.3), rand(T, Hs), zeros(Hs)
+    S3 = zeros(Hs, 128, 64)
+    timed("state_space_scan", Hs, 128, 64, lambda: seqops.state_space_scan(xbc, dt, hb, hb, hb, S3, Hs, 1, 128, 64))
+    a, b, S4 = rand(T, H), rand(T, H), zeros(H, 128, 128)
+    timed("gated_delta_rule (closest model)", H, 128, 128, lambda: seqops.gated_delta_rule(q, k, v, a, b, bz, bz, S4, H, H, 128, 128))
+    return out
+
+
+def run_vuzinex(args, rank, world, local_rank):
+    """Prefill and decode throughput of the Vuzinex family at real layer sizes, beside the closest existing model -- the Zatorax stack of
+    the same width, depth and active feed-forward width (run_zatorax's configuration) -- through the same step function and slots; then
+    the recurrence kernels alone beside the closest model's."""
+    from crabml_b200 import CudaTensorDevice, vuzinex, zatorax
+    if rank != 0:
+        return
+    width = int(args.workload.split("-w")[1])
+    Tp, K, W = args.prefill_tokens, args.steps, args.warmup
+    rng = np.random.default_rng(SEED)
+    prompt = [int(v) for v in rng.integers(0, 32000, Tp)]
+    sampler = ClockSampler(local_rank); sampler.start()
+    out = {}
+    for name, mod, cls, raw in (("vuzinex", vuzinex, "VuzinexModel", vuzinex_bench_config(width)), ("zatorax", zatorax, "ZatoraxModel", zatorax_bench_config(width))):
+        conf = mod.parse_config(raw)
+        dev = CudaTensorDevice(local_rank, lazy=0)
+        kw = {"max_seq": Tp + K + W + 8} if name == "vuzinex" else {}
+        weights = mod.random_weights(conf, SEED)
+        model = getattr(mod, cls)(dev, conf, weights, "bfloat16", chunk=args.zatorax_chunk, **kw)
+        params = sum(int(np.prod(np.shape(a))) for a in weights.values())
+        del weights
+        out[name] = measure_seq_model(dev, model, prompt, K, W, params)
+        model.close()
+        if name == "vuzinex":
+            out["recurrence_kernels"] = time_recurrences(dev, width, min(Tp, 2048))
+        dev.close()
+    clocks = sampler.stop()
+    z = out["vuzinex"]
+    line = {"metric": "decode_tokens_per_s", "value": z["decode_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": z["decode_ms_per_token"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 matrices and product inputs, f32 everything else", "data": "synthetic",
+            "config": {"workload": args.workload, "model": vuzinex_bench_config(width), "prefill_tokens": Tp, "chunk": args.zatorax_chunk,
+                       "closest_model": {"family": "zatorax", "model": zatorax_bench_config(width)}},
+            "e2e": {"value": 1e3 / z["decode_wall_ms_per_token"], "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 32000 * 4},
+            "gpu_launches": int(z["decode_launches_per_token"] * K), "detail": out, "clocks": clocks}
+    print(json.dumps(line))
+
+
 def run_zatorax(args, rank, world, local_rank):
     """Prefill and decode throughput of the Zatorax family at real layer sizes, beside the closest existing model -- a llama stack of the
     same width, depth, head layout and ACTIVE feed-forward width (Q8_0 weights, its serving format) -- through each family's runner.
@@ -698,7 +793,7 @@ def main():
     ap.add_argument("--no-also", action="store_true", help="skip the second (Q4_0) measurement of the default run")
     ap.add_argument("--multi", default="sharded", choices=["sharded", "replicas"], help="N > 1: shard one token stream (strong scaling, default) or run N independent replicas")
     ap.add_argument("--comm", default="p2p", choices=["p2p", "nccl"], help="exchange transport of the sharded path: one-shot NVLink peer stores (default) or the NCCL baseline")
-    ap.add_argument("--zatorax-chunk", type=int, default=512, help="zatorax / meresun workloads: longest run of prompt tokens one pass takes")
+    ap.add_argument("--zatorax-chunk", type=int, default=512, help="zatorax / meresun / vuzinex workloads: longest run of prompt tokens one pass takes")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -709,6 +804,8 @@ def main():
         run_zatorax(args, rank, world, local_rank)
     elif args.workload.startswith("meresun-"):
         run_meresun(args, rank, world, local_rank)
+    elif args.workload.startswith("vuzinex-"):
+        run_vuzinex(args, rank, world, local_rank)
     elif args.workload.endswith("-prefill"):
         run_prefill(args, rank, world, local_rank)
     else:
