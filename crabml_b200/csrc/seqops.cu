@@ -285,8 +285,12 @@ static int short_conv_impl(cc_device* dev, const cc_view* x, const cc_view* w, c
         SEQ_F32(dev, tail, "short_conv tail");
         CC_REQUIRE(dev, view_len(tail) == (K - 1) * C, "short_conv: tail must be [K-1, C]");
     }
-    const int hs = head_size > 0 ? head_size : (int)C;
+    int hs = head_size > 0 ? head_size : (int)C;
     CC_REQUIRE(dev, C % hs == 0, "short_conv: head_size %d does not divide %lld channels", hs, (long long)C);
+    if (!unit_norm) {            // nothing ties the channels of a head together: a warp takes the widest run of at most 32 channels that divides C
+        hs = 32;
+        while (C % hs) hs--;
+    }
     if (bias) { SEQ_F32(dev, bias, "short_conv bias"); CC_REQUIRE(dev, view_len(bias) == C, "short_conv: the bias needs one number per channel"); }
     cc_buf* y = nullptr;
     int rc = cc_new_activation(dev, T * C, CC_F32, false, &y);
@@ -1026,8 +1030,11 @@ extern "C" CC_API int cc_group_rms_norm(cc_device* dev, const cc_view* dst, cons
     return CC_OK;
 }
 
-// the gate first, then the norm: one warp per (row, group)
-__global__ void gated_group_rms_norm_kernel(float* __restrict__ dst, const float* __restrict__ x, const float* __restrict__ gate, const float* __restrict__ w, int64_t n_units,
+// the gate first, then the norm.  One warp per (row, group), or one CTA of GGN_THREADS threads when a group is wide (a single warp would walk
+// it in many dependent trips to memory).  Either way the gated value is written once, its squares are summed in an order that depends on
+// the group's size alone (lane- or thread-strided partial sums, the butterfly, then the warps' sums in warp order), and the value is scaled.
+#define GGN_THREADS 256
+__global__ void gated_group_rms_norm_kernel(float* dst, const float* x, const float* __restrict__ gate, const float* __restrict__ w, int64_t n_units,
                                             int groups, int gs, float eps, int act) {
     const int64_t u = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
@@ -1035,12 +1042,31 @@ __global__ void gated_group_rms_norm_kernel(float* __restrict__ dst, const float
     const float* xr = x + u * gs;
     const float* gr = gate + u * gs;
     const float* wr = w + (u % groups) * gs;
+    float* dr = dst + u * gs;
     float ss = 0.0f;
-    for (int c = lane; c < gs; c += 32) { const float v = xr[c] * seq_act(gr[c], act); ss = fmaf(v, v, ss); }
+    for (int c = lane; c < gs; c += 32) { const float v = xr[c] * seq_act(gr[c], act); dr[c] = v; ss = fmaf(v, v, ss); }
     ss = warp_sum(ss);
     const float inv = 1.0f / sqrtf(ss / (float)gs + eps);
+    for (int c = lane; c < gs; c += 32) dr[c] = dr[c] * inv * wr[c];
+}
+__global__ void __launch_bounds__(GGN_THREADS) gated_group_rms_norm_wide_kernel(float* dst, const float* x, const float* __restrict__ gate,
+                                                                                const float* __restrict__ w, int groups, int gs, float eps, int act) {
+    __shared__ float red[GGN_THREADS / 32];
+    const int64_t u = blockIdx.x;
+    const float* xr = x + u * gs;
+    const float* gr = gate + u * gs;
+    const float* wr = w + (u % groups) * gs;
     float* dr = dst + u * gs;
-    for (int c = lane; c < gs; c += 32) dr[c] = xr[c] * seq_act(gr[c], act) * inv * wr[c];
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < gs; c += GGN_THREADS) { const float v = xr[c] * seq_act(gr[c], act); dr[c] = v; ss = fmaf(v, v, ss); }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.0f;
+#pragma unroll
+    for (int i = 0; i < GGN_THREADS / 32; i++) tot += red[i];
+    const float inv = 1.0f / sqrtf(tot / (float)gs + eps);
+    for (int c = threadIdx.x; c < gs; c += GGN_THREADS) dr[c] = dr[c] * inv * wr[c];
 }
 extern "C" CC_API int cc_gated_group_rms_norm(cc_device* dev, const cc_view* dst, const cc_view* x, const cc_view* gate, const cc_view* w, int32_t groups, float eps,
                                               int32_t gate_act) {
@@ -1053,7 +1079,9 @@ extern "C" CC_API int cc_gated_group_rms_norm(cc_device* dev, const cc_view* dst
                (long long)view_len(w));
     if (rows == 0) return CC_OK;
     const int64_t units = rows * groups;
-    gated_group_rms_norm_kernel<<<(unsigned)((units + 7) / 8), 256, 0, dev->stream>>>(fptr(dst), fptr(x), fptr(gate), fptr(w), units, groups, (int)(cols / groups), eps, gate_act);
+    const int gs = (int)(cols / groups);
+    if (gs >= 512) gated_group_rms_norm_wide_kernel<<<(unsigned)units, GGN_THREADS, 0, dev->stream>>>(fptr(dst), fptr(x), fptr(gate), fptr(w), groups, gs, eps, gate_act);
+    else gated_group_rms_norm_kernel<<<(unsigned)((units + 7) / 8), 256, 0, dev->stream>>>(fptr(dst), fptr(x), fptr(gate), fptr(w), units, groups, gs, eps, gate_act);
     CC_LAUNCH_CHECK(dev);
     return CC_OK;
 }

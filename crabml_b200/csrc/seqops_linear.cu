@@ -39,11 +39,15 @@ struct LrArgs {
     int vec;                      // rows of q / k / adec may be copied 16 bytes at a time
     float q_scale;
 };
-// grid (H, ceil(dv / columns per CTA)).  A column j of the head's state is owned for the whole call by SPLIT adjacent threads, each holding
-// dk / SPLIT of its entries: DK > 0 in registers, DK == 0 (any dk) in shared memory [dk][LR_THREADS].  k, q (and the channel decays) of
-// LR_TB tokens at a time are staged in shared memory by asynchronous copies issued one block ahead; per token a thread runs once over its
-// share:  S[i] = k[i] * (a v_j) + D[i] * S[i] ; out += S[i] * q[i]   as four interleaved partial sums added (p0 + p1) + (p2 + p3).
-#define LR_THREADS 64
+// grid (H, ceil(dv / columns per CTA)).  A column j of the head's state is owned for the whole call by SPLIT adjacent threads.  DK > 0
+// (dk = 32, 64, 128): a CTA is 32 columns x SPLIT threads, each thread keeps dk / SPLIT = 16 entries in registers -- the 4-float pieces
+// part, part + SPLIT, ... of the column, so that the SPLIT threads of a column read neighbouring pieces of k and q (no bank conflicts) -- and
+// the partial read-outs are added by a butterfly over the SPLIT lanes: a short dependent chain per token, many warps per CTA.  DK == 0 (any
+// dk): 64 columns, one thread each, the column in shared memory [dk][64].  k, q (and the channel decays) of LR_TB tokens at a time are staged
+// in shared memory by asynchronous copies issued one block ahead; per token a thread runs once over its share:
+//   S[i] = k[i] * (a v_j) + D[i] * S[i] ; out += S[i] * q[i]      as four interleaved partial sums added (p0 + p1) + (p2 + p3).
+#define LR_COLS 32
+#define LR_GENERIC_THREADS 64
 #define LR_TB 16
 __device__ __forceinline__ void lr_cp16(float* dst, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
@@ -51,63 +55,70 @@ __device__ __forceinline__ void lr_cp16(float* dst, const float* src) {
 __device__ __forceinline__ void lr_cp4(float* dst, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
-// one staging buffer: k[TB][dk4], q[TB][dk4], (adec[TB][dk4]), sc[TB][2], v[TB][LR_THREADS]
-static __host__ __device__ __forceinline__ int lr_stage_floats(int dk4, bool adec) { return (adec ? 3 : 2) * LR_TB * dk4 + 2 * LR_TB + LR_TB * LR_THREADS; }
+// one staging buffer: k[TB][dk4], q[TB][dk4], (adec[TB][dk4]), sc[TB][2], v[TB][cols]
+static __host__ __device__ __forceinline__ int lr_stage_floats(int dk4, bool adec, int cols) { return (adec ? 3 : 2) * LR_TB * dk4 + 2 * LR_TB + LR_TB * cols; }
 
 template <int DK, int SPLIT, bool ADEC>
-__global__ void __launch_bounds__(LR_THREADS) lr_kernel(LrArgs a) {
+__global__ void __launch_bounds__(DK > 0 ? LR_COLS * SPLIT : LR_GENERIC_THREADS) lr_kernel(LrArgs a) {
     extern __shared__ __align__(16) float lr_sm[];           // two staging buffers, then (DK == 0) the state columns
-    constexpr int DKP = DK > 0 ? DK / SPLIT : 1;
-    constexpr int COLS = LR_THREADS / SPLIT;
+    constexpr int THREADS = DK > 0 ? LR_COLS * SPLIT : LR_GENERIC_THREADS;
+    constexpr int COLS = THREADS / SPLIT;
+    constexpr int DKP = DK > 0 ? DK / SPLIT : 4;             // entries per thread (register path)
     const int dk = a.dk, dv = a.dv, T = a.T;
-    const int dk4 = (dk + 3) & ~3;
-    const int stage_floats = lr_stage_floats(dk4, ADEC);
+    const int dk4 = DK > 0 ? DK : (dk + 3) & ~3;
+    const int stage_floats = lr_stage_floats(dk4, ADEC, COLS);
     const int h = blockIdx.x, g = h / (a.H / a.G);
-    const int part = threadIdx.x % SPLIT;
-    const int j = blockIdx.y * COLS + threadIdx.x / SPLIT;
+    const int part = threadIdx.x % SPLIT, col = threadIdx.x / SPLIT;
+    const int j = blockIdx.y * COLS + col;
     const bool live = j < dv;
     const int jj = live ? j : dv - 1;                      // idle threads shadow the last column and never store
     const bool ones = jj >= a.v_hs;
-    float S[DKP];
-    float* Ss = lr_sm + 2 * stage_floats + threadIdx.x;     // generic: S[i] at Ss[i * LR_THREADS]
-    float* sp = a.state + ((int64_t)h * dk + part * DKP) * dv + jj;
+    float S[DKP];                                           // S[4 m + e] is row 4 (part + SPLIT m) + e of the column
+    float* Ss = lr_sm + 2 * stage_floats + threadIdx.x;     // generic: row i at Ss[i * THREADS]
+    float* sp = a.state + (int64_t)h * dk * dv + jj;
     if (DK > 0) {
 #pragma unroll
-        for (int i = 0; i < DKP; i++) S[i] = sp[(int64_t)i * dv];
+        for (int i = 0; i < DKP; i++) S[i] = sp[(int64_t)(4 * (part + SPLIT * (i >> 2)) + (i & 3)) * dv];
     } else {
-        for (int i = 0; i < dk4; i++) Ss[i * LR_THREADS] = i < dk ? sp[(int64_t)i * dv] : 0.0f;
+        for (int i = 0; i < dk4; i++) Ss[i * THREADS] = i < dk ? sp[(int64_t)i * dv] : 0.0f;
     }
     const int n_rows = (ADEC ? 3 : 2) * LR_TB;
     // the pad lanes dk .. dk4 of both buffers are zero for the whole call (the copies below never touch them)
     if (dk4 != dk)
-        for (int idx = threadIdx.x; idx < 2 * n_rows; idx += LR_THREADS)
+        for (int idx = threadIdx.x; idx < 2 * n_rows; idx += THREADS)
             for (int i = dk; i < dk4; i++) lr_sm[(idx / n_rows) * stage_floats + (idx % n_rows) * dk4 + i] = 0.0f;
     const float skip = a.skip ? a.skip[h] : 0.0f;
+    // a thread's first piece of a block of tokens, and how far the next one is: item idx = threadIdx.x + n THREADS is token idx / per,
+    // piece idx % per of the block; walked without divisions
+    const int per = a.vec ? dk >> 2 : dk, width = a.vec ? 4 : 1;
+    const int tt0 = threadIdx.x / per, c0 = threadIdx.x % per, dtt = THREADS / per, dc = THREADS % per;
     auto stage = [&](int buf, int tb) {
         float* base = lr_sm + buf * stage_floats;
         const int nt = min(LR_TB, T - tb);
-        if (a.vec) {
-            const int per = dk >> 2;
-            for (int idx = threadIdx.x; idx < nt * per; idx += LR_THREADS) {
-                const int tt = idx / per, c = (idx - tt * per) * 4;
-                lr_cp16(base + tt * dk4 + c, a.k + (int64_t)(tb + tt) * a.k_rs + g * dk + c);
-                lr_cp16(base + (LR_TB + tt) * dk4 + c, a.q + (int64_t)(tb + tt) * a.q_rs + g * dk + c);
-                if (ADEC) lr_cp16(base + (2 * LR_TB + tt) * dk4 + c, a.adec + ((int64_t)(tb + tt) * a.H + h) * dk + c);
+        for (int tt = tt0, c = c0; tt < nt;) {
+            const int e = c * width;
+            const float* ks = a.k + (int64_t)(tb + tt) * a.k_rs + g * dk + e;
+            const float* qs = a.q + (int64_t)(tb + tt) * a.q_rs + g * dk + e;
+            if (a.vec) {
+                lr_cp16(base + tt * dk4 + e, ks);
+                lr_cp16(base + (LR_TB + tt) * dk4 + e, qs);
+                if (ADEC) lr_cp16(base + (2 * LR_TB + tt) * dk4 + e, a.adec + ((int64_t)(tb + tt) * a.H + h) * dk + e);
+            } else {
+                lr_cp4(base + tt * dk4 + e, ks);
+                lr_cp4(base + (LR_TB + tt) * dk4 + e, qs);
+                if (ADEC) lr_cp4(base + (2 * LR_TB + tt) * dk4 + e, a.adec + ((int64_t)(tb + tt) * a.H + h) * dk + e);
             }
-        } else {
-            for (int idx = threadIdx.x; idx < nt * dk; idx += LR_THREADS) {
-                const int tt = idx / dk, c = idx - tt * dk;
-                lr_cp4(base + tt * dk4 + c, a.k + (int64_t)(tb + tt) * a.k_rs + g * dk + c);
-                lr_cp4(base + (LR_TB + tt) * dk4 + c, a.q + (int64_t)(tb + tt) * a.q_rs + g * dk + c);
-                if (ADEC) lr_cp4(base + (2 * LR_TB + tt) * dk4 + c, a.adec + ((int64_t)(tb + tt) * a.H + h) * dk + c);
-            }
+            tt += dtt; c += dc;
+            if (c >= per) { c -= per; tt++; }
         }
         float* ssc = base + n_rows * dk4;
         if (a.sc)
-            for (int idx = threadIdx.x; idx < nt * 2; idx += LR_THREADS) lr_cp4(ssc + idx, a.sc + ((int64_t)(tb + (idx >> 1)) * a.H + h) * 2 + (idx & 1));
-        if (!ones) {
-            float* sv = ssc + 2 * LR_TB + threadIdx.x;
-            for (int tt = 0; tt < nt; tt++) lr_cp4(sv + tt * LR_THREADS, a.v + (int64_t)(tb + tt) * a.v_rs + h * a.v_hs + jj);
+            for (int idx = threadIdx.x; idx < nt * 2; idx += THREADS) lr_cp4(ssc + idx, a.sc + ((int64_t)(tb + (idx >> 1)) * a.H + h) * 2 + (idx & 1));
+        // the block's values of the CTA's columns: [token][column]
+        float* sv = ssc + 2 * LR_TB;
+        for (int idx = threadIdx.x; idx < nt * COLS; idx += THREADS) {
+            const int tt = idx / COLS, cc = idx % COLS, jc = blockIdx.y * COLS + cc;
+            if (jc < a.v_hs) lr_cp4(sv + idx, a.v + (int64_t)(tb + tt) * a.v_rs + h * a.v_hs + jc);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -120,23 +131,26 @@ __global__ void __launch_bounds__(LR_THREADS) lr_kernel(LrArgs a) {
         if (tb + LR_TB < T) stage(buf ^ 1, tb + LR_TB);
         const float* base = lr_sm + buf * stage_floats;
         const float* ssc = base + n_rows * dk4;
-        const float* sv = ssc + 2 * LR_TB + threadIdx.x;
-#pragma unroll 1
-        for (int tt = 0; tt < nt; tt++) {
-            const float* kt = base + tt * dk4 + part * DKP;
-            const float* qt = base + (LR_TB + tt) * dk4 + part * DKP;
-            const float* dt = base + (2 * LR_TB + tt) * dk4 + part * DKP;
+        const float* sv = ssc + 2 * LR_TB + col;
+        float* op = a.out + ((int64_t)tb * a.H + h) * dv + j;
+        const int64_t o_rs = (int64_t)a.H * dv;
+        // one token.  Only S ties a token to the one before it: in the unrolled loop of a full block the loads and the read-out's butterfly of
+        // neighbouring tokens overlap
+        auto token = [&](int tt) {
+            const float* kt = base + tt * dk4 + 4 * part;
+            const float* qt = base + (LR_TB + tt) * dk4 + 4 * part;
+            const float* dt = base + (2 * LR_TB + tt) * dk4 + 4 * part;
             const float dec = a.sc ? ssc[tt * 2] : 1.0f, wgt = a.sc ? ssc[tt * 2 + 1] : 1.0f;
-            const float vj = ones ? 1.0f : sv[tt * LR_THREADS];
+            const float vj = ones ? 1.0f : sv[tt * COLS];
             const float u = wgt * vj;
             float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
             if (DK > 0) {
 #pragma unroll
                 for (int i = 0; i < DKP; i += 4) {
-                    const float4 kv = *(const float4*)(kt + i);
-                    const float4 qv = *(const float4*)(qt + i);
+                    const float4 kv = *(const float4*)(kt + SPLIT * i);
+                    const float4 qv = *(const float4*)(qt + SPLIT * i);
                     float4 dd = make_float4(dec, dec, dec, dec);
-                    if (ADEC) dd = *(const float4*)(dt + i);
+                    if (ADEC) dd = *(const float4*)(dt + SPLIT * i);
                     S[i] = fmaf(kv.x, u, dd.x * S[i]); S[i + 1] = fmaf(kv.y, u, dd.y * S[i + 1]); S[i + 2] = fmaf(kv.z, u, dd.z * S[i + 2]); S[i + 3] = fmaf(kv.w, u, dd.w * S[i + 3]);
                     o0 = fmaf(S[i], qv.x, o0); o1 = fmaf(S[i + 1], qv.y, o1); o2 = fmaf(S[i + 2], qv.z, o2); o3 = fmaf(S[i + 3], qv.w, o3);
                 }
@@ -146,24 +160,32 @@ __global__ void __launch_bounds__(LR_THREADS) lr_kernel(LrArgs a) {
                     const float4 qv = *(const float4*)(qt + i);
                     float4 dd = make_float4(dec, dec, dec, dec);
                     if (ADEC) dd = *(const float4*)(dt + i);
-                    const float s0 = fmaf(kv.x, u, dd.x * Ss[i * LR_THREADS]), s1 = fmaf(kv.y, u, dd.y * Ss[(i + 1) * LR_THREADS]);
-                    const float s2 = fmaf(kv.z, u, dd.z * Ss[(i + 2) * LR_THREADS]), s3 = fmaf(kv.w, u, dd.w * Ss[(i + 3) * LR_THREADS]);
-                    Ss[i * LR_THREADS] = s0; Ss[(i + 1) * LR_THREADS] = s1; Ss[(i + 2) * LR_THREADS] = s2; Ss[(i + 3) * LR_THREADS] = s3;
+                    const float s0 = fmaf(kv.x, u, dd.x * Ss[i * THREADS]), s1 = fmaf(kv.y, u, dd.y * Ss[(i + 1) * THREADS]);
+                    const float s2 = fmaf(kv.z, u, dd.z * Ss[(i + 2) * THREADS]), s3 = fmaf(kv.w, u, dd.w * Ss[(i + 3) * THREADS]);
+                    Ss[i * THREADS] = s0; Ss[(i + 1) * THREADS] = s1; Ss[(i + 2) * THREADS] = s2; Ss[(i + 3) * THREADS] = s3;
                     o0 = fmaf(s0, qv.x, o0); o1 = fmaf(s1, qv.y, o1); o2 = fmaf(s2, qv.z, o2); o3 = fmaf(s3, qv.w, o3);
                 }
             }
             float outv = (o0 + o1) + (o2 + o3);
-            if (SPLIT == 2) outv += __shfl_xor_sync(0xffffffffu, outv, 1);
+#pragma unroll
+            for (int mask = 1; mask < SPLIT; mask <<= 1) outv += __shfl_xor_sync(0xffffffffu, outv, mask);
             outv = fmaf(skip, vj, outv * a.q_scale);
-            if (live && part == 0) a.out[((int64_t)(tb + tt) * a.H + h) * dv + j] = outv;
+            if (live && part == 0) op[tt * o_rs] = outv;
+        };
+        if (nt == LR_TB) {
+#pragma unroll 4
+            for (int tt = 0; tt < LR_TB; tt++) token(tt);
+        } else {
+#pragma unroll 1
+            for (int tt = 0; tt < nt; tt++) token(tt);
         }
     }
     if (live) {
         if (DK > 0) {
 #pragma unroll
-            for (int i = 0; i < DKP; i++) sp[(int64_t)i * dv] = S[i];
+            for (int i = 0; i < DKP; i++) sp[(int64_t)(4 * (part + SPLIT * (i >> 2)) + (i & 3)) * dv] = S[i];
         } else {
-            for (int i = 0; i < dk; i++) sp[(int64_t)i * dv] = Ss[i * LR_THREADS];
+            for (int i = 0; i < dk; i++) sp[(int64_t)i * dv] = Ss[i * THREADS];
         }
     }
 }
@@ -174,20 +196,19 @@ static cudaError_t lr_launch_one(cc_device* dev, const LrArgs& a, size_t smem) {
         cudaError_t e = cudaFuncSetAttribute(lr_kernel<DK, SPLIT, ADEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    const int cols = LR_THREADS / SPLIT;
-    lr_kernel<DK, SPLIT, ADEC><<<dim3((unsigned)a.H, (unsigned)((a.dv + cols - 1) / cols)), LR_THREADS, smem, dev->stream>>>(a);
+    const int threads = DK > 0 ? LR_COLS * SPLIT : LR_GENERIC_THREADS, cols = threads / SPLIT;
+    lr_kernel<DK, SPLIT, ADEC><<<dim3((unsigned)a.H, (unsigned)((a.dv + cols - 1) / cols)), threads, smem, dev->stream>>>(a);
     return cudaGetLastError();
 }
 template <bool ADEC>
 static int lr_launch_sized(cc_device* dev, const LrArgs& a, const char* what) {
     const int dk4 = (a.dk + 3) & ~3;
-    const size_t stage = (size_t)2 * lr_stage_floats(dk4, ADEC) * 4;
     cudaError_t e;
-    if (a.dk == 32) e = lr_launch_one<32, 1, ADEC>(dev, a, stage);
-    else if (a.dk == 64) e = lr_launch_one<64, 1, ADEC>(dev, a, stage);
-    else if (a.dk == 128) e = lr_launch_one<128, 2, ADEC>(dev, a, stage);
-    else {
-        const size_t smem = stage + (size_t)dk4 * LR_THREADS * 4;
+    if (a.dk == 32 || a.dk == 64 || a.dk == 128) {
+        const size_t stage = (size_t)2 * lr_stage_floats(dk4, ADEC, LR_COLS) * 4;
+        e = a.dk == 32 ? lr_launch_one<32, 2, ADEC>(dev, a, stage) : a.dk == 64 ? lr_launch_one<64, 4, ADEC>(dev, a, stage) : lr_launch_one<128, 8, ADEC>(dev, a, stage);
+    } else {
+        const size_t smem = (size_t)2 * lr_stage_floats(dk4, ADEC, LR_GENERIC_THREADS) * 4 + (size_t)dk4 * LR_GENERIC_THREADS * 4;
         if (smem > 200 * 1024) return cc_fail(dev, CC_ERR_UNSUPPORTED, "%s: a state of %d rows per head is too large", what, a.dk);
         e = lr_launch_one<0, 1, ADEC>(dev, a, smem);
     }
