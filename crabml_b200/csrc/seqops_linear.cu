@@ -42,7 +42,8 @@ struct LrArgs {
 // grid (H, ceil(dv / columns per CTA)).  A column j of the head's state is owned for the whole call by SPLIT adjacent threads.  DK > 0
 // (dk = 32, 64, 128): a CTA is 32 columns x SPLIT threads, each thread keeps dk / SPLIT = 16 entries in registers -- the 4-float pieces
 // part, part + SPLIT, ... of the column, so that the SPLIT threads of a column read neighbouring pieces of k and q (no bank conflicts) -- and
-// the partial read-outs are added by a butterfly over the SPLIT lanes: a short dependent chain per token, many warps per CTA.  DK == 0 (any
+// the lanes' partial read-outs of a block of tokens go to shared memory and are added after the block, parts in ascending order: a short
+// dependent chain per token with no shuffle in it, many warps per CTA.  DK == 0 (any
 // dk): 64 columns, one thread each, the column in shared memory [dk][64].  k, q (and the channel decays) of LR_TB tokens at a time are staged
 // in shared memory by asynchronous copies issued one block ahead; per token a thread runs once over its share:
 //   S[i] = k[i] * (a v_j) + D[i] * S[i] ; out += S[i] * q[i]      as four interleaved partial sums added (p0 + p1) + (p2 + p3).
@@ -75,6 +76,7 @@ __global__ void __launch_bounds__(DK > 0 ? LR_COLS * SPLIT : LR_GENERIC_THREADS)
     const bool ones = jj >= a.v_hs;
     float S[DKP];                                           // S[4 m + e] is row 4 (part + SPLIT m) + e of the column
     float* Ss = lr_sm + 2 * stage_floats + threadIdx.x;     // generic: row i at Ss[i * THREADS]
+    float* pbuf = lr_sm + 2 * stage_floats;                 // SPLIT > 1: the lanes' partial read-outs of a block of tokens, [token][column][part]
     float* sp = a.state + (int64_t)h * dk * dv + jj;
     if (DK > 0) {
 #pragma unroll
@@ -167,10 +169,12 @@ __global__ void __launch_bounds__(DK > 0 ? LR_COLS * SPLIT : LR_GENERIC_THREADS)
                 }
             }
             float outv = (o0 + o1) + (o2 + o3);
-#pragma unroll
-            for (int mask = 1; mask < SPLIT; mask <<= 1) outv += __shfl_xor_sync(0xffffffffu, outv, mask);
-            outv = fmaf(skip, vj, outv * a.q_scale);
-            if (live && part == 0) op[tt * o_rs] = outv;
+            if (SPLIT > 1) {
+                pbuf[tt * THREADS + threadIdx.x] = outv;           // added up after the block: no shuffle waits between tokens
+            } else {
+                outv = fmaf(skip, vj, outv * a.q_scale);
+                if (live) op[tt * o_rs] = outv;
+            }
         };
         if (nt == LR_TB) {
 #pragma unroll 4
@@ -178,6 +182,20 @@ __global__ void __launch_bounds__(DK > 0 ? LR_COLS * SPLIT : LR_GENERIC_THREADS)
         } else {
 #pragma unroll 1
             for (int tt = 0; tt < nt; tt++) token(tt);
+        }
+        if (SPLIT > 1) {
+            // the block's read-outs: a column's SPLIT parts added in ascending order, one order whatever T is
+            __syncthreads();
+            for (int idx = threadIdx.x; idx < nt * COLS; idx += THREADS) {
+                const int tt = idx / COLS, cc = idx % COLS, jc = blockIdx.y * COLS + cc;
+                if (jc >= dv) continue;
+                const float* pp = pbuf + idx * SPLIT;
+                float sum = pp[0];
+#pragma unroll
+                for (int e = 1; e < SPLIT; e++) sum += pp[e];
+                const float vj = jc >= a.v_hs ? 1.0f : ssc[2 * LR_TB + tt * COLS + cc];
+                a.out[((int64_t)(tb + tt) * a.H + h) * dv + jc] = fmaf(skip, vj, sum * a.q_scale);
+            }
         }
     }
     if (live) {
@@ -205,7 +223,8 @@ static int lr_launch_sized(cc_device* dev, const LrArgs& a, const char* what) {
     const int dk4 = (a.dk + 3) & ~3;
     cudaError_t e;
     if (a.dk == 32 || a.dk == 64 || a.dk == 128) {
-        const size_t stage = (size_t)2 * lr_stage_floats(dk4, ADEC, LR_COLS) * 4;
+        const int split = a.dk / 16;
+        const size_t stage = (size_t)2 * lr_stage_floats(dk4, ADEC, LR_COLS) * 4 + (size_t)LR_TB * LR_COLS * split * 4;
         e = a.dk == 32 ? lr_launch_one<32, 2, ADEC>(dev, a, stage) : a.dk == 64 ? lr_launch_one<64, 4, ADEC>(dev, a, stage) : lr_launch_one<128, 8, ADEC>(dev, a, stage);
     } else {
         const size_t smem = (size_t)2 * lr_stage_floats(dk4, ADEC, LR_GENERIC_THREADS) * 4 + (size_t)dk4 * LR_GENERIC_THREADS * 4;
