@@ -53,9 +53,10 @@ def main(argv=None):
             want = list(e.get("want", []))
             if not e["tokens"]:
                 continue
-            lg = model.step(slots[rid], e["tokens"], want)
+            places = sorted(set(int(i) for i in want))               # the step function takes ascending places; the file keeps the entry's order
+            lg = model.step(slots[rid], e["tokens"], places)
             if want:
-                rows.append(lg)
+                rows.append(lg[[places.index(int(i)) for i in want]])
         for rid in st.get("end", []):
             if rid in slots:
                 model.close_seq(slots.pop(rid))
