@@ -120,6 +120,25 @@ class cvr_layer_weights(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in CVR_WEIGHT_FIELDS]
 
 
+class clr_layer_config(C.Structure):            # include/crabml_lifesun.h
+    _fields_ = [(n, C.c_int32) for n in ("heads", "kv_heads", "dim", "vdim", "window", "block", "qk_norm", "left_gate")] + [("scale", C.c_float), ("softcap", C.c_float)] + \
+               [(n, C.c_int32) for n in ("right", "r_width", "r_blocks", "r_conv", "r_heads", "r_dim", "r_vdim")] + \
+               [(n, C.c_float) for n in ("r_rate", "left_scale", "right_scale")] + [("ff", C.c_int32)]
+
+
+class clr_config(C.Structure):
+    _fields_ = [("n_layers", C.c_int32), ("width", C.c_int32), ("vocab", C.c_int32), ("norm_eps", C.c_float), ("logit_scale", C.c_float)] + \
+               [(n, C.c_int32) for n in ("loop_start", "loop_stop", "loop_times", "chunk", "max_seq")]
+
+
+CLR_WEIGHT_FIELDS = ("norm_w", "norm_b", "h_stack", "q_norm", "k_norm", "sink", "rot_freq", "left_o", "right_o", "x_bias", "y_bias", "conv", "conv_bias", "gate_w", "gate_b",
+                     "lam", "r_rot_freq", "decay", "down")
+
+
+class clr_layer_weights(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in CLR_WEIGHT_FIELDS]
+
+
 class cc_route_params(C.Structure):              # include/crabml_seqops.h
     _fields_ = [(n, C.c_int32) for n in ("score", "top", "n_groups", "keep_groups", "group_top", "renormalise")] + [("renorm_eps", C.c_float)]
 
@@ -251,6 +270,14 @@ def load_library(build_if_missing: bool = True):
         "cc_matrix_memory": (i32, [vp, pv, pv, pv, pv, pv, pv, pv, f32, f32, pv, pv, i32, i32, i32, pp]),
         "cc_decayed_linear_attention": (i32, [vp, pv, pv, pv, pv, pv, f32, f32, pv, i32, i32, i32, pp]),
         "cc_state_space_scan": (i32, [vp, pv, pv, pv, pv, pv, pv, i32, i32, i32, i32, pp]),
+        "cc_layer_norm": (i32, [vp, pv, pv, pv, pv, f32]),
+        "cc_head_gate": (i32, [vp, pv, pv, i32, i32]),
+        "cc_concat_cols": (i32, [vp, pv, pv, pp]),
+        "cc_rope_halves": (i32, [vp, pv, i32, i32, i32, pv, f32, i64]),
+        "cc_masked_attention_capped": (i32, [vp, pv, pv, pv, i64, i32, i32, i32, i32, i32, i32, f32, f32, pv, pp]),
+        "cc_retention": (i32, [vp, pv, pv, pv, pv, f32, pv, i32, i32, i32, pp]),
+        "cc_gated_diagonal_recurrence": (i32, [vp, pv, pv, pv, pv, f32, i32, pv, pv, i32, pv, pp]),
+        "clr_runner_create": (i32, [vp, C.POINTER(clr_config), C.POINTER(clr_layer_config), C.POINTER(clr_layer_weights), vp, vp, vp, vp, vp, pp]),
         "cvr_runner_create": (i32, [vp, C.POINTER(cvr_config), C.POINTER(cvr_layer_config), C.POINTER(cvr_layer_weights), vp, vp, vp, vp, pp]),
         "csr_runner_destroy": (None, [vp]),
         "csr_runner_last_error": (C.c_char_p, [vp]),

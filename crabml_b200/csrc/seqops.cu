@@ -192,6 +192,47 @@ extern "C" CC_API int cc_scaled_sum(cc_device* dev, const cc_view* dst, const cc
     return CC_OK;
 }
 
+// one gate number per (row, head): one thread per element
+__global__ void head_gate_kernel(float* __restrict__ x, const float* __restrict__ g, int64_t n, int hs, int act) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] *= seq_act(g[i / hs], act);
+}
+extern "C" CC_API int cc_head_gate(cc_device* dev, const cc_view* x, const cc_view* g, int32_t n_heads, int32_t act) {
+    SEQ_ENTER(dev, "head_gate");
+    SEQ_F32(dev, x, "head_gate x"); SEQ_F32(dev, g, "head_gate g");
+    CC_REQUIRE(dev, x->ndim == 2 && n_heads > 0 && x->shape[1] % n_heads == 0 && view_len(g) == x->shape[0] * n_heads,
+               "head_gate: x must be [rows, heads * head_size] and g [rows, heads]");
+    const int64_t n = view_len(x);
+    if (!n) return CC_OK;
+    head_gate_kernel<<<(unsigned)((n + 255) / 256), 256, 0, dev->stream>>>(fptr(x), fptr(g), n, (int)(x->shape[1] / n_heads), act);
+    CC_LAUNCH_CHECK(dev);
+    return CC_OK;
+}
+// out = [a | b] row by row: one thread per element of out
+__global__ void concat_cols_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out, int64_t n, int ca, int cb) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int64_t r = i / (ca + cb);
+    const int c = (int)(i - r * (ca + cb));
+    out[i] = c < ca ? a[r * ca + c] : b[r * cb + (c - ca)];
+}
+extern "C" CC_API int cc_concat_cols(cc_device* dev, const cc_view* a, const cc_view* b, cc_buf** out) {
+    SEQ_ENTER(dev, "concat_cols");
+    if (!out) return cc_fail(dev, CC_ERR_ARG, "concat_cols: out is NULL");
+    SEQ_F32(dev, a, "concat_cols a"); SEQ_F32(dev, b, "concat_cols b");
+    CC_REQUIRE(dev, a->ndim == 2 && b->ndim == 2 && a->shape[0] == b->shape[0], "concat_cols: a and b must be [rows, ca] and [rows, cb]");
+    const int64_t rows = a->shape[0], ca = a->shape[1], cb = b->shape[1];
+    cc_buf* o = nullptr;
+    int rc = cc_new_activation(dev, rows * (ca + cb), CC_F32, false, &o);
+    if (rc) return rc;
+    *out = o;
+    const int64_t n = rows * (ca + cb);
+    if (!n) return CC_OK;
+    concat_cols_kernel<<<(unsigned)((n + 255) / 256), 256, 0, dev->stream>>>(fptr(a), fptr(b), (float*)o->base, n, (int)ca, (int)cb);
+    CC_LAUNCH_CHECK(dev);
+    return CC_OK;
+}
+
 // ---- a second embedding row chosen by a hash of the token pair ------------------------------------------------------------------------
 // one thread per (token, column); the hash is taken in 64-bit integers
 __global__ void pair_hash_rows_add_kernel(float* __restrict__ dst, const float* __restrict__ table, const int64_t* __restrict__ tok, const int32_t* __restrict__ last, int64_t n,
@@ -569,6 +610,7 @@ extern "C" CC_API int cc_kv_ring_append(cc_device* dev, const cc_view* kring, co
 struct WaGeom {
     int T, H, G, R, dk, dv, window, block, ring, QT, cap;      // QT queries per tile; cap = row stride of S; block > 0: a query sees only its own block of positions
     int krs, vrs, vhs;                                  // floats between two rows of the key / value ring (vhs: between two heads' values inside a row)
+    float softcap;                                      // > 0: score <- softcap * tanh(score / softcap), after the scale
     int64_t pos0;
 };
 __host__ __device__ __forceinline__ int64_t wa_lo(const WaGeom& g, int64_t i) {
@@ -655,6 +697,7 @@ __global__ void __launch_bounds__(WA_THREADS) wa_scores_kernel(const float* __re
             const int64_t j = j0 + tx * 4 + b;
             if (j < lo || j > i) continue;
             float sc = acc[a][b] * scale;
+            if (g.softcap > 0.0f) sc = g.softcap * tanhf(sc / g.softcap);
             if (r1) sc -= r1[h] * log1pf(r2[h] * (float)(i - j));
             Sr[j - lo] = sc;
         }
@@ -682,6 +725,7 @@ __global__ void __launch_bounds__(256) wa_scores_row_kernel(const float* __restr
         if (lane == 0) {
             const int h = kvh * g.R + hr;
             float sc = acc * scale;
+            if (g.softcap > 0.0f) sc = g.softcap * tanhf(sc / g.softcap);
             if (r1) sc -= r1[h] * log1pf(r2[h] * (float)(i - j));
             S[((int64_t)t * g.H + h) * g.cap + (j - lo)] = sc;
         }
@@ -899,7 +943,8 @@ __global__ void __launch_bounds__(WA_THREADS) wa_values_kernel(const float* __re
     }
 }
 static int masked_attention_impl(cc_device* dev, const cc_view* q, const cc_view* qnw, float eps, const cc_view* kring, const cc_view* vring, int64_t pos0, int32_t H, int32_t G,
-                                 int32_t dk, int32_t dv, int32_t window, int32_t block, float scale, const cc_view* r1, const cc_view* r2, const cc_view* sink, cc_buf** out) {
+                                 int32_t dk, int32_t dv, int32_t window, int32_t block, float scale, const cc_view* r1, const cc_view* r2, const cc_view* sink, cc_buf** out,
+                                 float softcap = 0.0f) {
     SEQ_ENTER(dev, "window_attention");
     if (!out) return cc_fail(dev, CC_ERR_ARG, "window_attention: out is NULL");
     SEQ_F32(dev, q, "window_attention q"); SEQ_F32(dev, kring, "window_attention kring");
@@ -919,7 +964,7 @@ static int masked_attention_impl(cc_device* dev, const cc_view* q, const cc_view
     // the oldest row the first query needs must not have been overwritten by the newest row of this call
     const int64_t last = pos0 + T - 1;
     WaGeom g;
-    g.window = window; g.block = block;
+    g.window = window; g.block = block; g.softcap = softcap;
     const int64_t oldest = wa_lo(g, pos0);
     CC_REQUIRE(dev, T == 0 || last - oldest + 1 <= ring, "window_attention: positions %lld..%lld with window %d, block %d need more than the ring's %lld rows",
                (long long)pos0, (long long)last, window, block, (long long)ring);
@@ -995,6 +1040,10 @@ extern "C" CC_API int cc_masked_attention(cc_device* dev, const cc_view* q, cons
                                           int32_t window, int32_t block, float scale, const cc_view* sink, cc_buf** out) {
     return masked_attention_impl(dev, q, nullptr, 0.0f, kring, vring, pos0, H, G, dk, dv, window, block, scale, nullptr, nullptr, sink, out);
 }
+extern "C" CC_API int cc_masked_attention_capped(cc_device* dev, const cc_view* q, const cc_view* kring, const cc_view* vring, int64_t pos0, int32_t H, int32_t G, int32_t dk,
+                                                 int32_t dv, int32_t window, int32_t block, float scale, float softcap, const cc_view* sink, cc_buf** out) {
+    return masked_attention_impl(dev, q, nullptr, 0.0f, kring, vring, pos0, H, G, dk, dv, window, block, scale, nullptr, nullptr, sink, out, softcap);
+}
 extern "C" CC_API int cc_window_attention(cc_device* dev, const cc_view* q, const cc_view* qnw, float eps, const cc_view* kring, const cc_view* vring, int64_t pos0,
                                           int32_t H, int32_t G, int32_t dk, int32_t dv, int32_t window, float scale, const cc_view* r1, const cc_view* r2,
                                           cc_buf** out) {
@@ -1026,6 +1075,39 @@ extern "C" CC_API int cc_group_rms_norm(cc_device* dev, const cc_view* dst, cons
     if (rows == 0) return CC_OK;
     const int64_t units = rows * groups;
     group_rms_norm_kernel<<<(unsigned)((units + 7) / 8), 256, 0, dev->stream>>>(fptr(dst), fptr(x), fptr(w), units, groups, (int)(cols / groups), eps);
+    CC_LAUNCH_CHECK(dev);
+    return CC_OK;
+}
+
+// ---- layer norm with weight and bias ------------------------------------------------------------------------------------------------------
+// one warp per row: the mean first (lane-strided partial sums, the butterfly), then the mean of the squared deviations from it in the same
+// order, then the scaled write.  The order depends on the row's length alone.
+__global__ void layer_norm_kernel(float* dst, const float* x, const float* __restrict__ w, const float* __restrict__ b, int64_t rows, int cols, float eps) {
+    const int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (r >= rows) return;
+    const float* xr = x + r * cols;
+    float s = 0.0f;
+    for (int c = lane; c < cols; c += 32) s += xr[c];
+    const float mean = warp_sum(s) / (float)cols;
+    float ss = 0.0f;
+    for (int c = lane; c < cols; c += 32) { const float d = xr[c] - mean; ss = fmaf(d, d, ss); }
+    const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)cols + eps);
+    float* dr = dst + r * cols;
+    for (int c = lane; c < cols; c += 32) {
+        const float v = (xr[c] - mean) * inv * w[c];
+        dr[c] = b ? v + b[c] : v;
+    }
+}
+extern "C" CC_API int cc_layer_norm(cc_device* dev, const cc_view* dst, const cc_view* x, const cc_view* w, const cc_view* b, float eps) {
+    SEQ_ENTER(dev, "layer_norm");
+    SEQ_F32(dev, dst, "layer_norm dst"); SEQ_F32(dev, x, "layer_norm x"); SEQ_F32(dev, w, "layer_norm w");
+    if (b) SEQ_F32(dev, b, "layer_norm b");
+    CC_REQUIRE(dev, x->ndim == 2 && dst->ndim == 2 && dst->shape[0] == x->shape[0] && dst->shape[1] == x->shape[1], "layer_norm: dst and x must be [rows, cols]");
+    const int64_t rows = x->shape[0], cols = x->shape[1];
+    CC_REQUIRE(dev, cols >= 1 && view_len(w) == cols && (!b || view_len(b) == cols), "layer_norm: %lld columns need as many weights (and biases)", (long long)cols);
+    if (rows == 0) return CC_OK;
+    layer_norm_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, dev->stream>>>(fptr(dst), fptr(x), fptr(w), b ? fptr(b) : nullptr, rows, (int)cols, eps);
     CC_LAUNCH_CHECK(dev);
     return CC_OK;
 }
@@ -1095,17 +1177,27 @@ __device__ __forceinline__ void rotate_pair(float u, float v, float pos, float f
     ov = v * c + u * s;
 }
 // one thread per (token, head, pair)
-__global__ void rope_pairs_kernel(float* __restrict__ x, const float* __restrict__ freq, int64_t n, int heads, int hs, int off, int half, float mag, int64_t pos0) {
+// pair i of a head is the columns off + i * step and off + i * step + gap: (step, gap) = (2, 1) pairs neighbours, (1, half) pairs the two
+// halves of the rotated columns
+__global__ void rope_pairs_kernel(float* __restrict__ x, const float* __restrict__ freq, int64_t n, int heads, int hs, int off, int half, float mag, int64_t pos0, int step,
+                                  int gap) {
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= n) return;
     const int i = (int)(idx % half);
     const int64_t th = idx / half;                                   // token * heads + head
-    float* p = x + th * hs + off + 2 * i;
+    float* p = x + th * hs + off + step * i;
     float ou, ov;
-    rotate_pair(p[0], p[1], (float)(pos0 + th / heads), freq[i], mag, ou, ov);
-    p[0] = ou; p[1] = ov;
+    rotate_pair(p[0], p[gap], (float)(pos0 + th / heads), freq[i], mag, ou, ov);
+    p[0] = ou; p[gap] = ov;
 }
+static int rope_table_impl(cc_device* dev, const cc_view* x, int32_t n_heads, int32_t head_size, int32_t offset, const cc_view* freq, float mag, int64_t pos0, bool halves);
 extern "C" CC_API int cc_rope_pairs(cc_device* dev, const cc_view* x, int32_t n_heads, int32_t head_size, int32_t offset, const cc_view* freq, float mag, int64_t pos0) {
+    return rope_table_impl(dev, x, n_heads, head_size, offset, freq, mag, pos0, false);
+}
+extern "C" CC_API int cc_rope_halves(cc_device* dev, const cc_view* x, int32_t n_heads, int32_t head_size, int32_t offset, const cc_view* freq, float mag, int64_t pos0) {
+    return rope_table_impl(dev, x, n_heads, head_size, offset, freq, mag, pos0, true);
+}
+static int rope_table_impl(cc_device* dev, const cc_view* x, int32_t n_heads, int32_t head_size, int32_t offset, const cc_view* freq, float mag, int64_t pos0, bool halves) {
     SEQ_ENTER(dev, "rope_pairs");
     SEQ_F32(dev, x, "rope_pairs x"); SEQ_F32(dev, freq, "rope_pairs freq");
     const int64_t half = view_len(freq);
@@ -1113,7 +1205,8 @@ extern "C" CC_API int cc_rope_pairs(cc_device* dev, const cc_view* x, int32_t n_
                "rope_pairs: %lld pairs at column %d do not fit heads of %d", (long long)half, offset, head_size);
     const int64_t n = x->shape[0] * n_heads * half;
     if (n == 0) return CC_OK;
-    rope_pairs_kernel<<<(unsigned)((n + 255) / 256), 256, 0, dev->stream>>>(fptr(x), fptr(freq), n, n_heads, head_size, offset, (int)half, mag, pos0);
+    rope_pairs_kernel<<<(unsigned)((n + 255) / 256), 256, 0, dev->stream>>>(fptr(x), fptr(freq), n, n_heads, head_size, offset, (int)half, mag, pos0, halves ? 1 : 2,
+                                                                            halves ? (int)half : 1);
     CC_LAUNCH_CHECK(dev);
     return CC_OK;
 }

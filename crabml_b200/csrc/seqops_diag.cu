@@ -1,0 +1,116 @@
+// seqops_diag.cu -- the gated diagonal recurrence of include/crabml_seqops.h (the real-gated linear recurrent unit): a state of one number per
+// channel that every token first shrinks by a gate-dependent decay and then adds a gated, rescaled input to,
+//     r = sigmoid(g_r + b_r) ; i = sigmoid(g_i + b_i) ; log a = -c r softplus(lam)
+//     S <- a S + sqrt(1 - a^2) (i u) ; out = S * act(y + y_b)
+// Everything is 32-bit (expf / log1pf / expm1f / tanhf of the CUDA math library).  1 - a^2 is taken as -expm1(2 log a): for a decay close to
+// one the difference 1 - a * a would lose most of its digits.
+//
+// Only S ties a token to the one before it, and the tie is one fused multiply-add.  So the work is split: all warps of a CTA turn a block of
+// tokens into the pairs (a, sqrt(1 - a^2) i u) side by side, one warp then walks the block in order, and all warps write the gated
+// read-outs.  A token's result depends on its inputs and the state alone; the order of the walk is the order of the tokens, whatever the
+// call carries, so prompts, portions and decoding give the same bits.
+#include "../../include/crabml_seqops.h"
+#include "capi_checks.cuh"
+
+#define DG_ENTER(dev, what)                                                                                           \
+    if (!(dev)) return CC_ERR_ARG;                                                                                    \
+    CC_ENTER(dev);                                                                                                    \
+    if (LAZY(dev)) return cc_fail((dev), CC_ERR_UNSUPPORTED, "%s: not available on a lazy (graph / megakernel) device", what)
+#define DG_F32(dev, v, what)                                                                                           \
+    do {                                                                                                              \
+        if (!view_ok(v)) return cc_fail((dev), CC_ERR_ARG, "%s: bad tensor view", what);                              \
+        if (!view_in_bounds(v)) return cc_fail((dev), CC_ERR_TENSOR, "%s: view addresses element %lld of a buffer of %lld", what, \
+                                               (long long)view_max_offset(v), (long long)(v)->buf->nelems);           \
+        CC_REQUIRE(dev, view_contiguous(v), "%s: not contiguous", what);                                              \
+        REQUIRE_F32(dev, v, what);                                                                                    \
+    } while (0)
+static inline float* dptr(const cc_view* v) { return (float*)v->buf->plane[0]; }
+
+__device__ __forceinline__ float dg_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float dg_softplus(float z) { return fmaxf(z, 0.0f) + log1pf(expf(-fabsf(z))); }
+__device__ __forceinline__ float dg_act(float z, int act) {
+    return act == CC_ACT_SILU        ? z / (1.0f + expf(-z))
+           : act == CC_ACT_GELU_TANH ? 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)))
+           : act == CC_ACT_SIGMOID   ? dg_sigmoid(z)
+                                     : z;
+}
+
+#define DG_CH 32            // channels of a CTA: one lane each
+#define DG_WARPS 8
+#define DG_TB 32            // tokens per block
+struct DgArgs {
+    const float *u, *gates, *gate_bias, *lam, *y, *y_bias;
+    float *state, *out;
+    int T, C, bs;           // bs: channels per gate block
+    int y_act;
+    float c;
+};
+// grid ceil(C / 32), 8 warps.  Lane l of every warp is channel blockIdx.x * 32 + l.
+__global__ void __launch_bounds__(DG_CH* DG_WARPS) gated_diag_kernel(DgArgs a) {
+    __shared__ float s_a[DG_TB][DG_CH], s_b[DG_TB][DG_CH], s_s[DG_TB][DG_CH];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int ch = blockIdx.x * DG_CH + lane;
+    const bool live = ch < a.C;
+    const int cc = live ? ch : a.C - 1;                       // idle lanes shadow the last channel and never store
+    const int blk = cc / a.bs, o = cc - blk * a.bs;
+    const int col_r = blk * 2 * a.bs + o, col_i = col_r + a.bs;
+    const float br = a.gate_bias[col_r], bi = a.gate_bias[col_i];
+    const float rate = a.c * dg_softplus(a.lam[cc]);
+    const float yb = a.y_bias ? a.y_bias[cc] : 0.0f;
+    float S = w == 0 ? a.state[cc] : 0.0f;
+    for (int tb = 0; tb < a.T; tb += DG_TB) {
+        const int nt = min(DG_TB, a.T - tb);
+        for (int tt = w; tt < nt; tt += DG_WARPS) {
+            const int64_t t = tb + tt;
+            const float* gr = a.gates + t * 2 * a.C;
+            const float r = dg_sigmoid(gr[col_r] + br), i = dg_sigmoid(gr[col_i] + bi);
+            const float la = -(rate * r);
+            s_a[tt][lane] = expf(la);
+            s_b[tt][lane] = sqrtf(-expm1f(2.0f * la)) * (i * a.u[t * a.C + cc]);
+        }
+        __syncthreads();
+        if (w == 0) {
+#pragma unroll 8
+            for (int tt = 0; tt < nt; tt++) {
+                S = fmaf(s_a[tt][lane], S, s_b[tt][lane]);
+                s_s[tt][lane] = S;
+            }
+        }
+        __syncthreads();
+        if (live)
+            for (int tt = w; tt < nt; tt += DG_WARPS) {
+                const int64_t t = tb + tt;
+                float v = s_s[tt][lane];
+                if (a.y) v *= dg_act(a.y[t * a.C + ch] + yb, a.y_act);
+                a.out[t * a.C + ch] = v;
+            }
+    }
+    if (w == 0 && live) a.state[ch] = S;
+}
+
+extern "C" CC_API int cc_gated_diagonal_recurrence(cc_device* dev, const cc_view* u, const cc_view* gates, const cc_view* gate_bias, const cc_view* lam, float c,
+                                                   int32_t n_blocks, const cc_view* y, const cc_view* y_bias, int32_t y_act, const cc_view* state, cc_buf** out) {
+    DG_ENTER(dev, "gated_diagonal_recurrence");
+    if (!out) return cc_fail(dev, CC_ERR_ARG, "gated_diagonal_recurrence: out is NULL");
+    DG_F32(dev, u, "gated_diagonal_recurrence u"); DG_F32(dev, gates, "gated_diagonal_recurrence gates"); DG_F32(dev, gate_bias, "gated_diagonal_recurrence gate_bias");
+    DG_F32(dev, lam, "gated_diagonal_recurrence lam"); DG_F32(dev, state, "gated_diagonal_recurrence state");
+    if (y) DG_F32(dev, y, "gated_diagonal_recurrence y");
+    if (y_bias) DG_F32(dev, y_bias, "gated_diagonal_recurrence y_bias");
+    CC_REQUIRE(dev, u->ndim == 2 && u->shape[1] >= 1 && n_blocks >= 1 && u->shape[1] % n_blocks == 0, "gated_diagonal_recurrence: u must be [T, C] with C a multiple of the %d blocks",
+               n_blocks);
+    const int64_t T = u->shape[0], C = u->shape[1];
+    CC_REQUIRE(dev, view_len(gates) == 2 * T * C && view_len(gate_bias) == 2 * C && view_len(lam) == C && view_len(state) == C && (!y || view_len(y) == T * C) &&
+                        (!y_bias || (y && view_len(y_bias) == C)),
+               "gated_diagonal_recurrence: operand sizes do not fit T=%lld channels=%lld", (long long)T, (long long)C);
+    cc_buf* o = nullptr;
+    int rc = cc_new_activation(dev, T * C, CC_F32, false, &o);
+    if (rc) return rc;
+    *out = o;
+    if (T == 0) return CC_OK;
+    DgArgs a{};
+    a.u = dptr(u); a.gates = dptr(gates); a.gate_bias = dptr(gate_bias); a.lam = dptr(lam); a.y = y ? dptr(y) : nullptr; a.y_bias = y_bias ? dptr(y_bias) : nullptr;
+    a.state = dptr(state); a.out = (float*)o->base; a.T = (int)T; a.C = (int)C; a.bs = (int)(C / n_blocks); a.y_act = y_act; a.c = c;
+    gated_diag_kernel<<<(unsigned)((C + DG_CH - 1) / DG_CH), DG_CH * DG_WARPS, 0, dev->stream>>>(a);
+    CC_LAUNCH_CHECK(dev);
+    return CC_OK;
+}

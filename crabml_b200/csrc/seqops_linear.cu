@@ -1,7 +1,8 @@
 // seqops_linear.cu -- linear recurrences over a matrix state (include/crabml_seqops.h): the matrix memory with exponential gates, linear
 // attention with a decay per key channel, and the selective state-space scan.  All three are
 //     S <- D_t S + a_t k_t v_t^T ;  out_t = S^T q_t                 S: [dk, dv] per head, F32, carried between calls
-// with D_t a number per (token, head) or a vector over the key channels, and a_t a number per (token, head).  One kernel runs that form
+// with D_t a number per (token, head), a fixed number per head or a vector over the key channels, and a_t a number per (token, head) or one
+// constant.  One kernel runs that form
 // (lr_kernel); a small kernel per mixer turns raw projections into D_t and a_t first, in 32-bit floats (expf / log1pf / tanhf of the CUDA
 // math library).  The matrix memory's normaliser n_t = D_t n + a_t k_t is one more column of the state whose value is 1 for every token.
 //
@@ -32,6 +33,8 @@ struct LrArgs {
     const float *q, *k, *v;       // q, k: row t at + t * rs, the head group's dk numbers at + g * dk; v: row t at + t * v_rs, head h's at + h * v_hs
     const float* adec;            // [T, H * dk] decay per key channel, or NULL
     const float* sc;              // [T, H, 2] = {decay, weight of the outer product} per (token, head), or NULL (1, 1)
+    const float* hdec;            // [H] one decay per head for every token, or NULL (1); read only when sc is NULL
+    float wgt;                    // weight of the outer product when sc is NULL
     const float* skip;            // [H] or NULL: out += skip[h] * v
     float *state, *out;           // state [H, dk, dv]; out [T, H, dv]
     int T, H, G, dk, dv;          // dv: columns of the state
@@ -90,6 +93,7 @@ __global__ void __launch_bounds__(DK > 0 ? LR_COLS * SPLIT : LR_GENERIC_THREADS)
         for (int idx = threadIdx.x; idx < 2 * n_rows; idx += THREADS)
             for (int i = dk; i < dk4; i++) lr_sm[(idx / n_rows) * stage_floats + (idx % n_rows) * dk4 + i] = 0.0f;
     const float skip = a.skip ? a.skip[h] : 0.0f;
+    const float head_dec = a.hdec ? a.hdec[h] : 1.0f;
     // a thread's first piece of a block of tokens, and how far the next one is: item idx = threadIdx.x + n THREADS is token idx / per,
     // piece idx % per of the block; walked without divisions
     const int per = a.vec ? dk >> 2 : dk, width = a.vec ? 4 : 1;
@@ -142,7 +146,7 @@ __global__ void __launch_bounds__(DK > 0 ? LR_COLS * SPLIT : LR_GENERIC_THREADS)
             const float* kt = base + tt * dk4 + 4 * part;
             const float* qt = base + (LR_TB + tt) * dk4 + 4 * part;
             const float* dt = base + (2 * LR_TB + tt) * dk4 + 4 * part;
-            const float dec = a.sc ? ssc[tt * 2] : 1.0f, wgt = a.sc ? ssc[tt * 2 + 1] : 1.0f;
+            const float dec = a.sc ? ssc[tt * 2] : head_dec, wgt = a.sc ? ssc[tt * 2 + 1] : a.wgt;
             const float vj = ones ? 1.0f : sv[tt * COLS];
             const float u = wgt * vj;
             float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
@@ -311,7 +315,7 @@ extern "C" CC_API int cc_matrix_memory(cc_device* dev, const cc_view* q, const c
     dev->launches++;
     LrArgs a{};
     a.q = lptr(q); a.k = lptr(k); a.v = lptr(v); a.adec = nullptr; a.sc = sc; a.skip = nullptr; a.state = lptr(state); a.out = raw;
-    a.T = (int)T; a.H = H; a.G = H; a.dk = dk; a.dv = dv + 1; a.q_rs = a.k_rs = H * dk; a.v_rs = H * dv; a.v_hs = dv; a.q_scale = q_scale;
+    a.T = (int)T; a.H = H; a.G = H; a.dk = dk; a.dv = dv + 1; a.q_rs = a.k_rs = H * dk; a.v_rs = H * dv; a.v_hs = dv; a.q_scale = q_scale; a.wgt = 1.0f;
     rc = lr_launch(dev, a, "matrix_memory");
     if (rc == CC_OK) {
         const int64_t n = T * H * dv;
@@ -353,9 +357,34 @@ extern "C" CC_API int cc_decayed_linear_attention(cc_device* dev, const cc_view*
     dev->launches++;
     LrArgs a{};
     a.q = lptr(q); a.k = lptr(k); a.v = lptr(v); a.adec = (const float*)tmp; a.sc = nullptr; a.skip = nullptr; a.state = lptr(state); a.out = (float*)o->base;
-    a.T = (int)T; a.H = H; a.G = H; a.dk = dk; a.dv = dv; a.q_rs = a.k_rs = H * dk; a.v_rs = H * dv; a.v_hs = dv; a.q_scale = q_scale;
+    a.T = (int)T; a.H = H; a.G = H; a.dk = dk; a.dv = dv; a.q_rs = a.k_rs = H * dk; a.v_rs = H * dv; a.v_hs = dv; a.q_scale = q_scale; a.wgt = 1.0f;
     rc = lr_launch(dev, a, "decayed_linear_attention");
     cc_pool_free(dev, tmp, cls);
+    if (rc) return rc;
+    CC_LAUNCH_CHECK(dev);
+    return CC_OK;
+}
+
+// ---- retention: a fixed decay per head -------------------------------------------------------------------------------------------------------
+extern "C" CC_API int cc_retention(cc_device* dev, const cc_view* q, const cc_view* k, const cc_view* v, const cc_view* decay, float k_scale, const cc_view* state, int32_t H,
+                                   int32_t dk, int32_t dv, cc_buf** out) {
+    LIN_ENTER(dev, "retention");
+    if (!out) return cc_fail(dev, CC_ERR_ARG, "retention: out is NULL");
+    LIN_F32(dev, q, "retention q"); LIN_F32(dev, k, "retention k"); LIN_F32(dev, v, "retention v"); LIN_F32(dev, decay, "retention decay"); LIN_F32(dev, state, "retention state");
+    CC_REQUIRE(dev, H > 0 && dk > 0 && dv > 0 && q->ndim == 2, "retention: bad head counts / sizes");
+    const int64_t T = q->shape[0];
+    CC_REQUIRE(dev, view_len(q) == T * H * dk && view_len(k) == T * H * dk && view_len(v) == T * H * dv && view_len(decay) == H && view_len(state) == (int64_t)H * dk * dv,
+               "retention: operand sizes do not fit T=%lld heads=%d dk=%d dv=%d", (long long)T, H, dk, dv);
+    cc_buf* o = nullptr;
+    int rc = cc_new_activation(dev, T * H * dv, CC_F32, false, &o);
+    if (rc) return rc;
+    *out = o;
+    if (T == 0) return CC_OK;
+    LrArgs a{};
+    a.q = lptr(q); a.k = lptr(k); a.v = lptr(v); a.adec = nullptr; a.sc = nullptr; a.hdec = lptr(decay); a.wgt = k_scale; a.skip = nullptr; a.state = lptr(state);
+    a.out = (float*)o->base;
+    a.T = (int)T; a.H = H; a.G = H; a.dk = dk; a.dv = dv; a.q_rs = a.k_rs = H * dk; a.v_rs = H * dv; a.v_hs = dv; a.q_scale = 1.0f;
+    rc = lr_launch(dev, a, "retention");
     if (rc) return rc;
     CC_LAUNCH_CHECK(dev);
     return CC_OK;
@@ -397,7 +426,7 @@ extern "C" CC_API int cc_state_space_scan(cc_device* dev, const cc_view* xbc, co
     const float* base = lptr(xbc);
     a.v = base; a.k = base + (int64_t)H * P; a.q = base + (int64_t)H * P + (int64_t)G * N; a.adec = nullptr; a.sc = (const float*)tmp;
     a.skip = d_skip ? lptr(d_skip) : nullptr; a.state = lptr(state); a.out = (float*)o->base;
-    a.T = (int)T; a.H = H; a.G = G; a.dk = N; a.dv = P; a.q_rs = a.k_rs = a.v_rs = (int)row; a.v_hs = P; a.q_scale = 1.0f;
+    a.T = (int)T; a.H = H; a.G = G; a.dk = N; a.dv = P; a.q_rs = a.k_rs = a.v_rs = (int)row; a.v_hs = P; a.q_scale = 1.0f; a.wgt = 1.0f;
     rc = lr_launch(dev, a, "state_space_scan");
     cc_pool_free(dev, tmp, cls);
     if (rc) return rc;

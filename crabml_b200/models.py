@@ -62,3 +62,11 @@ def _load_vuzinex(path, device, dtype="bfloat16", chunk=0, max_tokens=0, **_):
 
 
 register("Vuzinex", _load_vuzinex)
+
+
+def _load_lifesun(path, device, dtype="bfloat16", chunk=0, max_tokens=0, **_):
+    from . import lifesun
+    return lifesun.load(path, device, dtype, chunk, max_tokens)
+
+
+register("Lifesun", _load_lifesun)

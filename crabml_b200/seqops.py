@@ -219,3 +219,46 @@ def state_space_scan(xbc, dt, dt_bias, a_log, d_skip, state, n_heads, n_groups, 
     xbc.device.check(xbc.device.lib.cc_state_space_scan(xbc.device.handle, _v(xbc), _v(dt), _v(dt_bias), _v(a_log), _v(d_skip), _v(state), n_heads, n_groups, n_state,
                                                         head_dim, C.byref(h)))
     return _new(xbc.device, h, [xbc.shape()[0], n_heads * head_dim])
+
+
+def layer_norm(x, w, b, eps, dst=None):
+    dst = dst if dst is not None else type(x).alloc(x.shape(), capi.F32, x.device)
+    x.device.check(x.device.lib.cc_layer_norm(x.device.handle, _v(dst), _v(x), _v(w), _v(b), float(eps)))
+    return dst
+
+
+def head_gate(x, g, n_heads, act=capi.ACT_SIGMOID):
+    x.device.check(x.device.lib.cc_head_gate(x.device.handle, _v(x), _v(g), int(n_heads), int(act)))
+    return x
+
+
+def concat_cols(a, b):
+    h = C.c_void_p()
+    a.device.check(a.device.lib.cc_concat_cols(a.device.handle, _v(a), _v(b), C.byref(h)))
+    return _new(a.device, h, [a.shape()[0], a.shape()[1] + b.shape()[1]])
+
+
+def rope_halves(x, n_heads, head_size, offset, freq, mag, pos0):
+    x.device.check(x.device.lib.cc_rope_halves(x.device.handle, _v(x), int(n_heads), int(head_size), int(offset), _v(freq), float(mag), int(pos0)))
+    return x
+
+
+def masked_attention_capped(q, kring, vring, pos0, n_heads, n_kv, dk, dv, scale, window=0, block=0, softcap=0.0, sink=None):
+    h = C.c_void_p()
+    q.device.check(q.device.lib.cc_masked_attention_capped(q.device.handle, _v(q), _v(kring), _v(vring), int(pos0), n_heads, n_kv, dk, dv, int(window), int(block),
+                                                           float(scale), float(softcap), _v(sink), C.byref(h)))
+    return _new(q.device, h, [q.shape()[0], n_heads * dv])
+
+
+def retention(q, k, v, decay, k_scale, state, n_heads, dk, dv):
+    h = C.c_void_p()
+    q.device.check(q.device.lib.cc_retention(q.device.handle, _v(q), _v(k), _v(v), _v(decay), float(k_scale), _v(state), n_heads, dk, dv, C.byref(h)))
+    return _new(q.device, h, [q.shape()[0], n_heads * dv])
+
+
+def gated_diagonal_recurrence(u, gates, gate_bias, lam, c, n_blocks, state, y=None, y_bias=None, y_act=capi.ACT_NONE):
+    """gates / gate_bias: per block of channels the recurrence gate followed by the input gate, [n_blocks][2][C / n_blocks]"""
+    h = C.c_void_p()
+    u.device.check(u.device.lib.cc_gated_diagonal_recurrence(u.device.handle, _v(u), _v(gates), _v(gate_bias), _v(lam), float(c), int(n_blocks), _v(y), _v(y_bias),
+                                                             int(y_act), _v(state), C.byref(h)))
+    return _new(u.device, h, list(u.shape()))

@@ -42,6 +42,9 @@ CC_API int cc_gated_head_rms_norm(cc_device* dev, const cc_view* x, const cc_vie
 /* dst[r] = x[r] with every one of `groups` equal consecutive parts of the row divided by its own sqrt(mean(part^2) + eps), times w[:]
  * (w: cols numbers).  groups = 1 is the plain weighted RMS norm.  dst may be x. */
 CC_API int cc_group_rms_norm(cc_device* dev, const cc_view* dst, const cc_view* x, const cc_view* w, int32_t groups, float eps);
+/* Layer norm with weight and bias: dst[r] = (x[r] - mean) / sqrt(var + eps) * w + b, var the mean of the squared deviations from the
+ * mean.  dst, x: [rows, cols]; w, b: [cols] (b NULL: no bias).  dst may be x. */
+CC_API int cc_layer_norm(cc_device* dev, const cc_view* dst, const cc_view* x, const cc_view* w, const cc_view* b, float eps);
 /* dst = x * act(gate) with every one of `groups` equal consecutive parts of the row then divided by its own root mean square, times w[:]:
  * the gate comes BEFORE the norm (cc_gated_head_rms_norm gates after it).  All [rows, cols]; w: [cols].  dst may be x. */
 CC_API int cc_gated_group_rms_norm(cc_device* dev, const cc_view* dst, const cc_view* x, const cc_view* gate, const cc_view* w, int32_t groups, float eps,
@@ -66,6 +69,10 @@ CC_API int cc_glu_halves(cc_device* dev, const cc_view* src, const cc_view* bias
 CC_API int cc_add_row_bias(cc_device* dev, const cc_view* x, const cc_view* bias);
 /* dst = sa * a + sb * b, elementwise (two branches that read one input, joined with fixed weights); dst may be a or b */
 CC_API int cc_scaled_sum(cc_device* dev, const cc_view* dst, const cc_view* a, float sa, const cc_view* b, float sb);
+/* x[t, h, :] *= act(g[t, h]): ONE gate number per (row, head) on the head's whole output.  x: [rows, heads * head_size], g: [rows, heads]. */
+CC_API int cc_head_gate(cc_device* dev, const cc_view* x, const cc_view* g, int32_t n_heads, int32_t act);
+/* out = [a | b], row by row: a [rows, ca], b [rows, cb] -> out [rows, ca + cb] (two streams that enter one product side by side) */
+CC_API int cc_concat_cols(cc_device* dev, const cc_view* a, const cc_view* b, cc_buf** out);
 
 /* ---- a second embedding row chosen by a hash of the token pair ------------------------------------------------------------------ */
 /* dst[t] += table[row_t], row_t = (prev_t * mul_prev + token_t * mul_cur) mod buckets, where prev_t is the token before token_t in the
@@ -123,6 +130,10 @@ CC_API int cc_window_attention_sink(cc_device* dev, const cc_view* q, const cc_v
  * given (both limits hold); both <= 0: every j <= i. */
 CC_API int cc_masked_attention(cc_device* dev, const cc_view* q, const cc_view* kring, const cc_view* vring, int64_t pos0, int32_t n_heads, int32_t n_kv, int32_t dk,
                                int32_t dv, int32_t window, int32_t block, float scale, const cc_view* sink, cc_buf** out);
+/* cc_masked_attention with a cap on the scores: softcap > 0 turns score into softcap * tanh(score / softcap) (after the scale, before the
+ * softmax); softcap <= 0: no cap. */
+CC_API int cc_masked_attention_capped(cc_device* dev, const cc_view* q, const cc_view* kring, const cc_view* vring, int64_t pos0, int32_t n_heads, int32_t n_kv,
+                                      int32_t dk, int32_t dv, int32_t window, int32_t block, float scale, float softcap, const cc_view* sink, cc_buf** out);
 
 /* ---- linear recurrences over a matrix state -------------------------------------------------------------------------------------------
  * Three mixers share one form: per head a state S [dk, dv] (F32, carried between calls, zero at the start of a sequence) that every token
@@ -147,6 +158,22 @@ CC_API int cc_decayed_linear_attention(cc_device* dev, const cc_view* q, const c
  * out: [T, H * P]. */
 CC_API int cc_state_space_scan(cc_device* dev, const cc_view* xbc, const cc_view* dt, const cc_view* dt_bias, const cc_view* a_log, const cc_view* d_skip,
                                const cc_view* state, int32_t n_heads, int32_t n_groups, int32_t n_state, int32_t head_dim, cc_buf** out);
+/* Retention: linear attention with one fixed decay per head, no softmax and no denominator.  q, k: [T, H * dk], v: [T, H * dv];
+ * decay: [H]; state: [H, dk, dv].
+ *   S = decay[h] S + (k_scale k) v^T ; out = S^T q */
+CC_API int cc_retention(cc_device* dev, const cc_view* q, const cc_view* k, const cc_view* v, const cc_view* decay, float k_scale, const cc_view* state,
+                        int32_t n_heads, int32_t dk, int32_t dv, cc_buf** out);
+
+/* ---- gated diagonal recurrence ----------------------------------------------------------------------------------------------------------
+ * The real-gated linear recurrent unit (RG-LRU of Griffin): a state of one number per channel, S [C] (F32, carried between calls, zero at
+ * the start of a sequence).  u: [T, C] the recurrence's input; gates: [T, 2 C] raw gate projections laid out as n_blocks equal blocks of
+ * channels, each block's recurrence gate followed by its input gate ([n_blocks][2][C / n_blocks], what one product per block of the stacked
+ * matrices [W_r,b ; W_i,b] leaves); gate_bias: [2 C] in the same layout; lam: [C].
+ *   r = sigmoid(gate_r + bias) ; i = sigmoid(gate_i + bias) ; log a = -c r softplus(lam)
+ *   S = exp(log a) S + sqrt(1 - exp(2 log a)) (i u) ; out = S * act(y + y_bias)        (y: [T, C] or NULL: out = S; y_bias: [C] or NULL)
+ * Everything is 32-bit; 1 - a^2 is taken as -expm1(2 log a).  out: [T, C]. */
+CC_API int cc_gated_diagonal_recurrence(cc_device* dev, const cc_view* u, const cc_view* gates, const cc_view* gate_bias, const cc_view* lam, float c, int32_t n_blocks,
+                                        const cc_view* y, const cc_view* y_bias, int32_t y_act, const cc_view* state, cc_buf** out);
 
 /* ---- rotary positions from a frequency table ----------------------------------------------------------------------------------- */
 /* x: [T, n_heads * head_size], rows are positions pos0 .. ; freq: [P] one frequency per pair.  In every head the columns
@@ -154,6 +181,9 @@ CC_API int cc_state_space_scan(cc_device* dev, const cc_view* xbc, const cc_view
  *   (u, v) <- ((u cos a - v sin a) * mag, (v cos a + u sin a) * mag) ; all other columns stay.  In place.
  * The table carries whatever scaling of the frequencies a model uses (crabml_b200/rotary.py builds plain and YaRN tables). */
 CC_API int cc_rope_pairs(cc_device* dev, const cc_view* x, int32_t n_heads, int32_t head_size, int32_t offset, const cc_view* freq, float mag, int64_t pos0);
+/* The same rotation with another pairing: with P = len(freq), column offset + i turns together with column offset + i + P (i < P), the
+ * "two halves" layout; all other columns stay.  In place. */
+CC_API int cc_rope_halves(cc_device* dev, const cc_view* x, int32_t n_heads, int32_t head_size, int32_t offset, const cc_view* freq, float mag, int64_t pos0);
 
 /* ---- latent key/value cache --------------------------------------------------------------------------------------------------- */
 /* A cache row is [c | r]: c, `rank` numbers from which keys and values of all heads derive, and r, a rotated key part that all heads
