@@ -45,6 +45,9 @@ WORKLOADS = {
     # the Vuzinex family at the same layer sizes, beside the Zatorax stack of equal width and depth; see run_vuzinex
     "vuzinex-w1024": ("VUZINEX", "BF16", "BF16"),
     "vuzinex-w2048": ("VUZINEX", "BF16", "BF16"),
+    # the Lifesun family at the same layer sizes, beside the Vuzinex stack of equal width and depth; see run_lifesun
+    "lifesun-w1024": ("LIFESUN", "BF16", "BF16"),
+    "lifesun-w2048": ("LIFESUN", "BF16", "BF16"),
 }
 # dram bytes per megakernel launch from the committed ncu --set full capture (profiles/); None until captured
 TRAFFIC = {("llama2-7b-q8_0", 1): 7040893000 + 49879296}     # profiles/r02p_mega_ring_q8_0_ncu_raw.csv (mega_ring_kernel: dram__bytes_read.sum + dram__bytes_write.sum)
@@ -716,6 +719,109 @@ def run_vuzinex(args, rank, world, local_rank):
     print(json.dumps(line))
 
 
+def lifesun_bench_config(width: int, vocab: int = 32000):
+    """four layers, each run once, each with a dense feed-forward of 3 x width, so that depth and active feed-forward width equal the
+    Vuzinex stack's: windowed attention (1024 positions, half of every head rotated, capped scores) beside retention, and attention in blocks
+    of 1024 positions beside the gated diagonal recurrence (as wide as the model, gate blocks of 128 channels, 4 taps), alternating; the two
+    middle layers form a loop that runs once.  128-wide attention heads, 4 query heads per key head."""
+    H = width // 128
+    G = max(1, H // 4)
+    R = max(1, H // 2)
+    mlp = {"kind": "dense", "ff": 3 * width}
+    a = {"type": "parallel_2", "mlp": mlp,
+         "mixer": {"left": {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0, "rot": {"dims": 64, "base": 200000.0}, "mask": {"size": 1024}},
+                   "right": {"heads": R, "dim": 64, "vdim": 128, "decay": [1.0 - 0.5 ** (4.5 + h) for h in range(R)], "rot": {"dims": 64, "base": 10000.0}},
+                   "left_scale": 1.0, "right_scale": 1.0}}
+    b = {"type": "parallel", "mlp": mlp, "mixer": {"left": {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 1024}},
+                                                   "right": {"width": width, "blocks": width // 128, "conv": 4}, "left_scale": 1.0, "right_scale": 1.0}}
+    return {"architecture": "Lifesun", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_scale": 1.0, "loop": {"start": 1, "stop": 3, "times": 1}, "layers": [a, b, a, b]}
+
+
+def time_lifesun_recurrences(dev, width, T):
+    """The recurrence kernels of the Lifesun family alone at the bench's sizes, beside the like kernel of the closest model (linear attention
+    with a decay per key channel): device time of one call over T tokens, the rate at which state elements are updated, and for the diagonal
+    recurrence (one state number per channel: its bound is the traffic of its operands) the bytes it moves per second."""
+    from crabml_b200 import CudaTensor, capi, seqops
+    rng = np.random.default_rng(SEED)
+
+    def rand(*shape, scale=1.0):
+        return CudaTensor.new((rng.standard_normal(shape) * scale).astype(np.float32), list(shape), dev)
+
+    def zeros(*shape):
+        t = CudaTensor.alloc(list(shape), capi.F32, dev)
+        seqops.tensor_zero(t)
+        return t
+    H = max(1, width // 256)
+    out = {}
+
+    def timed(name, f, **what):
+        f()
+        dev.synchronize(); dev.timer_begin()
+        for _ in range(3):
+            f()
+        ms = dev.timer_end() / 3
+        out[name] = dict(what, tokens=T, ms=ms)
+        return ms
+    q, k, v = rand(T, H * 64, scale=0.1), rand(T, H * 64, scale=0.1), rand(T, H * 128)
+    decay, S = CudaTensor.new(np.asarray([1.0 - 0.5 ** (4.5 + h) for h in range(H)], np.float32), [H], dev), zeros(H, 64, 128)
+    ms = timed("retention", lambda: seqops.retention(q, k, v, decay, 0.125, S, H, 64, 128), heads=H, dk=64, dv=128)
+    out["retention"]["state_updates_per_s"] = T * H * 64 * 128 / (ms * 1e-3)
+    z2, zb, S2 = rand(T, H * 64), zeros(H * 64), zeros(H, 64, 128)
+    ms = timed("decayed_linear_attention (closest model)", lambda: seqops.decayed_linear_attention(q, k, v, z2, zb, 8.0, 0.125, S2, H, 64, 128), heads=H, dk=64, dv=128)
+    out["decayed_linear_attention (closest model)"]["state_updates_per_s"] = T * H * 64 * 128 / (ms * 1e-3)
+    C, B = width, width // 128
+    u, y, yb, lam, st = rand(T, C), rand(T, C), zeros(C), CudaTensor.new(rng.uniform(-5, -1, C).astype(np.float32), [C], dev), zeros(C)
+    gw, gb = rand(2 * C, C // B, scale=(C // B) ** -0.5), zeros(2 * C)
+    gates = seqops.head_project(u, gw, B)
+    ms = timed("gated_diagonal_recurrence", lambda: seqops.gated_diagonal_recurrence(u, gates, gb, lam, 8.0, B, st, y=y, y_bias=yb, y_act=capi.ACT_GELU_TANH), channels=C, blocks=B)
+    out["gated_diagonal_recurrence"].update(bytes=5 * T * C * 4, bytes_per_s=5 * T * C * 4 / (ms * 1e-3))
+    ms = timed("gate products of the diagonal recurrence (one per block, 32-bit)", lambda: seqops.head_project(u, gw, B), channels=C, blocks=B)
+    out["gate products of the diagonal recurrence (one per block, 32-bit)"]["flop_per_s"] = 2 * T * 2 * C * (C // B) / (ms * 1e-3)
+    xw, xb, tail = rand(C, 4), zeros(C), zeros(3, C)
+    timed("short_conv_bias (4 taps, no activation)", lambda: seqops.short_conv_bias(u, xw, xb, tail, act=capi.ACT_NONE), channels=C)
+    Hs = 2 * width // 64
+    xbc, dt, hb, S3 = rand(T, Hs * 64 + 256, scale=0.3), rand(T, Hs), zeros(Hs), zeros(Hs, 128, 64)
+    ms = timed("state_space_scan (closest model)", lambda: seqops.state_space_scan(xbc, dt, hb, hb, hb, S3, Hs, 1, 128, 64), heads=Hs, dk=128, dv=64)
+    out["state_space_scan (closest model)"]["state_updates_per_s"] = T * Hs * 128 * 64 / (ms * 1e-3)
+    return out
+
+
+def run_lifesun(args, rank, world, local_rank):
+    """Prefill and decode throughput of the Lifesun family at real layer sizes, beside the closest existing model -- the Vuzinex stack of
+    the same width, depth and feed-forward width (run_vuzinex's configuration) -- through the same step function and slots; then the
+    recurrence kernels alone beside the closest model's."""
+    from crabml_b200 import CudaTensorDevice, lifesun, vuzinex
+    if rank != 0:
+        return
+    width = int(args.workload.split("-w")[1])
+    Tp, K, W = args.prefill_tokens, args.steps, args.warmup
+    rng = np.random.default_rng(SEED)
+    prompt = [int(v) for v in rng.integers(0, 32000, Tp)]
+    sampler = ClockSampler(local_rank); sampler.start()
+    out = {}
+    for name, mod, cls, raw in (("lifesun", lifesun, "LifesunModel", lifesun_bench_config(width)), ("vuzinex", vuzinex, "VuzinexModel", vuzinex_bench_config(width))):
+        conf = mod.parse_config(raw)
+        dev = CudaTensorDevice(local_rank, lazy=0)
+        weights = mod.random_weights(conf, SEED)
+        model = getattr(mod, cls)(dev, conf, weights, "bfloat16", chunk=args.zatorax_chunk, max_seq=Tp + K + W + 8)
+        params = sum(int(np.prod(np.shape(a))) for a in weights.values())
+        del weights
+        out[name] = measure_seq_model(dev, model, prompt, K, W, params)
+        model.close()
+        if name == "lifesun":
+            out["recurrence_kernels"] = time_lifesun_recurrences(dev, width, min(Tp, 2048))
+        dev.close()
+    clocks = sampler.stop()
+    z = out["lifesun"]
+    line = {"metric": "decode_tokens_per_s", "value": z["decode_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": z["decode_ms_per_token"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 matrices and product inputs, f32 everything else", "data": "synthetic",
+            "config": {"workload": args.workload, "model": lifesun_bench_config(width), "prefill_tokens": Tp, "chunk": args.zatorax_chunk,
+                       "closest_model": {"family": "vuzinex", "model": vuzinex_bench_config(width)}},
+            "e2e": {"value": 1e3 / z["decode_wall_ms_per_token"], "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 32000 * 4},
+            "gpu_launches": int(z["decode_launches_per_token"] * K), "detail": out, "clocks": clocks}
+    print(json.dumps(line))
+
+
 def run_zatorax(args, rank, world, local_rank):
     """Prefill and decode throughput of the Zatorax family at real layer sizes, beside the closest existing model -- a llama stack of the
     same width, depth, head layout and ACTIVE feed-forward width (Q8_0 weights, its serving format) -- through each family's runner.
@@ -793,7 +899,7 @@ def main():
     ap.add_argument("--no-also", action="store_true", help="skip the second (Q4_0) measurement of the default run")
     ap.add_argument("--multi", default="sharded", choices=["sharded", "replicas"], help="N > 1: shard one token stream (strong scaling, default) or run N independent replicas")
     ap.add_argument("--comm", default="p2p", choices=["p2p", "nccl"], help="exchange transport of the sharded path: one-shot NVLink peer stores (default) or the NCCL baseline")
-    ap.add_argument("--zatorax-chunk", type=int, default=512, help="zatorax / meresun / vuzinex workloads: longest run of prompt tokens one pass takes")
+    ap.add_argument("--zatorax-chunk", type=int, default=512, help="zatorax / meresun / vuzinex / lifesun workloads: longest run of prompt tokens one pass takes")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -806,6 +912,8 @@ def main():
         run_meresun(args, rank, world, local_rank)
     elif args.workload.startswith("vuzinex-"):
         run_vuzinex(args, rank, world, local_rank)
+    elif args.workload.startswith("lifesun-"):
+        run_lifesun(args, rank, world, local_rank)
     elif args.workload.endswith("-prefill"):
         run_prefill(args, rank, world, local_rank)
     else:

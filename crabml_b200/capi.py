@@ -272,6 +272,7 @@ def load_library(build_if_missing: bool = True):
         "cc_state_space_scan": (i32, [vp, pv, pv, pv, pv, pv, pv, i32, i32, i32, i32, pp]),
         "cc_layer_norm": (i32, [vp, pv, pv, pv, pv, f32]),
         "cc_head_gate": (i32, [vp, pv, pv, i32, i32]),
+        "cc_scaled_sum_accumulate": (i32, [vp, pv, pv, f32, pv, f32, pv]),
         "cc_concat_cols": (i32, [vp, pv, pv, pp]),
         "cc_rope_halves": (i32, [vp, pv, i32, i32, i32, pv, f32, i64]),
         "cc_masked_attention_capped": (i32, [vp, pv, pv, pv, i64, i32, i32, i32, i32, i32, i32, f32, f32, pv, pp]),

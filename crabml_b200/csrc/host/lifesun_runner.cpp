@@ -184,16 +184,15 @@ struct Runner : csr_runner {
             CudaTensor yl = left_mixer(L, s.runs[ri], part, pos0);
             CudaTensor yr = L.c.right == CLR_RIGHT_DIAGONAL ? diagonal_mixer(L, s.runs[ri], part) : retention_mixer(L, s.runs[ri], part, pos0);
             cc_view ylv = yl.view(), yrv = yr.view(), xv = x.view();
-            check(cc_scaled_sum(dev, &ylv, &ylv, L.c.left_scale, &yrv, L.c.right_scale));
             if (L.i_ff >= 0) {
                 cc_view gv = part[L.i_ff].view();
                 cc_buf* b = nullptr;
                 check(cc_glu_halves(dev, &gv, nullptr, CC_ACT_GELU_TANH, &b));
                 CudaTensor yd = L.down.matmul_vec(adopt(b, {n, L.c.ff}));
                 cc_view ydv = yd.view();
-                check(cc_gated_sum(dev, &xv, 1, &ylv, nullptr, nullptr, &ydv, nullptr, nullptr));
+                check(cc_scaled_sum_accumulate(dev, &xv, &ylv, L.c.left_scale, &yrv, L.c.right_scale, &ydv));
             } else {
-                check(cc_gated_sum(dev, &xv, 1, &ylv, nullptr, nullptr, nullptr, nullptr, nullptr));
+                check(cc_scaled_sum_accumulate(dev, &xv, &ylv, L.c.left_scale, &yrv, L.c.right_scale, nullptr));
             }
             x = std::move(x).with_name("run:" + std::to_string(ri) + ":" + std::to_string(pos0));
         }

@@ -192,6 +192,25 @@ extern "C" CC_API int cc_scaled_sum(cc_device* dev, const cc_view* dst, const cc
     return CC_OK;
 }
 
+__global__ void scaled_sum_accumulate_kernel(float* __restrict__ dst, const float* __restrict__ a, float sa, const float* __restrict__ b, float sb, const float* __restrict__ c,
+                                             int64_t n) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float v = sa * a[i] + sb * b[i];
+    if (c) v += c[i];
+    dst[i] += v;
+}
+extern "C" CC_API int cc_scaled_sum_accumulate(cc_device* dev, const cc_view* dst, const cc_view* a, float sa, const cc_view* b, float sb, const cc_view* c) {
+    SEQ_ENTER(dev, "scaled_sum_accumulate");
+    SEQ_F32(dev, dst, "scaled_sum_accumulate dst"); SEQ_F32(dev, a, "scaled_sum_accumulate a"); SEQ_F32(dev, b, "scaled_sum_accumulate b");
+    if (c) SEQ_F32(dev, c, "scaled_sum_accumulate c");
+    const int64_t n = view_len(dst);
+    CC_REQUIRE(dev, view_len(a) == n && view_len(b) == n && (!c || view_len(c) == n), "scaled_sum_accumulate: sizes differ");
+    if (!n) return CC_OK;
+    scaled_sum_accumulate_kernel<<<(unsigned)((n + 255) / 256), 256, 0, dev->stream>>>(fptr(dst), fptr(a), sa, fptr(b), sb, c ? fptr(c) : nullptr, n);
+    CC_LAUNCH_CHECK(dev);
+    return CC_OK;
+}
 // one gate number per (row, head): one thread per element
 __global__ void head_gate_kernel(float* __restrict__ x, const float* __restrict__ g, int64_t n, int hs, int act) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -1080,24 +1099,52 @@ extern "C" CC_API int cc_group_rms_norm(cc_device* dev, const cc_view* dst, cons
 }
 
 // ---- layer norm with weight and bias ------------------------------------------------------------------------------------------------------
-// one warp per row: the mean first (lane-strided partial sums, the butterfly), then the mean of the squared deviations from it in the same
+// one CTA per row: a thread keeps its (up to LN_KEEP) elements of the row in registers, so the row is read once; the mean first
+// (thread-strided partial sums, the butterfly, then the warps' sums in warp order), then the mean of the squared deviations from it in the same
 // order, then the scaled write.  The order depends on the row's length alone.
-__global__ void layer_norm_kernel(float* dst, const float* x, const float* __restrict__ w, const float* __restrict__ b, int64_t rows, int cols, float eps) {
-    const int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
-    if (r >= rows) return;
-    const float* xr = x + r * cols;
+#define LN_THREADS 256
+#define LN_KEEP 8
+__device__ __forceinline__ float ln_block_sum(float v, float* red) {
+    v = warp_sum(v);
+    __syncthreads();                                         // red may still be read from the sum before
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.0f;
+#pragma unroll
+    for (int w = 0; w < LN_THREADS / 32; w++) t += red[w];
+    return t;
+}
+__global__ void __launch_bounds__(LN_THREADS) layer_norm_kernel(float* dst, const float* x, const float* __restrict__ w, const float* __restrict__ b, int cols, float eps) {
+    __shared__ float red[LN_THREADS / 32];
+    const float* xr = x + (int64_t)blockIdx.x * cols;
+    float* dr = dst + (int64_t)blockIdx.x * cols;
+    float keep[LN_KEEP];
     float s = 0.0f;
-    for (int c = lane; c < cols; c += 32) s += xr[c];
-    const float mean = warp_sum(s) / (float)cols;
-    float ss = 0.0f;
-    for (int c = lane; c < cols; c += 32) { const float d = xr[c] - mean; ss = fmaf(d, d, ss); }
-    const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)cols + eps);
-    float* dr = dst + r * cols;
-    for (int c = lane; c < cols; c += 32) {
-        const float v = (xr[c] - mean) * inv * w[c];
-        dr[c] = b ? v + b[c] : v;
+#pragma unroll
+    for (int e = 0; e < LN_KEEP; e++) {
+        const int c = threadIdx.x + e * LN_THREADS;
+        keep[e] = c < cols ? xr[c] : 0.0f;
+        s += keep[e];
     }
+    for (int c = threadIdx.x + LN_KEEP * LN_THREADS; c < cols; c += LN_THREADS) s += xr[c];
+    const float mean = ln_block_sum(s, red) / (float)cols;
+    float ss = 0.0f;
+#pragma unroll
+    for (int e = 0; e < LN_KEEP; e++) {
+        const int c = threadIdx.x + e * LN_THREADS;
+        const float d = keep[e] - mean;
+        if (c < cols) ss = fmaf(d, d, ss);
+    }
+    for (int c = threadIdx.x + LN_KEEP * LN_THREADS; c < cols; c += LN_THREADS) { const float d = xr[c] - mean; ss = fmaf(d, d, ss); }
+    const float inv = 1.0f / sqrtf(ln_block_sum(ss, red) / (float)cols + eps);
+    // a row wider than the registers hold is read again here, before any of it is overwritten by another thread: dst may be x, and thread t only
+    // ever touches columns t, t + 256, ...
+#pragma unroll
+    for (int e = 0; e < LN_KEEP; e++) {
+        const int c = threadIdx.x + e * LN_THREADS;
+        if (c < cols) { const float v = (keep[e] - mean) * inv * w[c]; dr[c] = b ? v + b[c] : v; }
+    }
+    for (int c = threadIdx.x + LN_KEEP * LN_THREADS; c < cols; c += LN_THREADS) { const float v = (xr[c] - mean) * inv * w[c]; dr[c] = b ? v + b[c] : v; }
 }
 extern "C" CC_API int cc_layer_norm(cc_device* dev, const cc_view* dst, const cc_view* x, const cc_view* w, const cc_view* b, float eps) {
     SEQ_ENTER(dev, "layer_norm");
@@ -1107,7 +1154,7 @@ extern "C" CC_API int cc_layer_norm(cc_device* dev, const cc_view* dst, const cc
     const int64_t rows = x->shape[0], cols = x->shape[1];
     CC_REQUIRE(dev, cols >= 1 && view_len(w) == cols && (!b || view_len(b) == cols), "layer_norm: %lld columns need as many weights (and biases)", (long long)cols);
     if (rows == 0) return CC_OK;
-    layer_norm_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, dev->stream>>>(fptr(dst), fptr(x), fptr(w), b ? fptr(b) : nullptr, rows, (int)cols, eps);
+    layer_norm_kernel<<<(unsigned)rows, LN_THREADS, 0, dev->stream>>>(fptr(dst), fptr(x), fptr(w), b ? fptr(b) : nullptr, (int)cols, eps);
     CC_LAUNCH_CHECK(dev);
     return CC_OK;
 }
@@ -1297,6 +1344,55 @@ __global__ void __launch_bounds__(128) head_project_kernel(const float* __restri
         if (lane == 0 && t0 + tt < T) out[((int64_t)(t0 + tt) * H + h) * os + v] = sum;
     }
 }
+// many rows and nothing carried: a 64 x 64 output tile of one head per CTA, 16-deep slices of the inputs through shared memory, 4 x 4 outputs
+// per thread, every sum over n_in in ascending order inside one thread.  grid (ceil(n_out / 64), ceil(T / 64), H)
+#define HPT_TILE 64
+#define HPT_K 16
+__global__ void __launch_bounds__(256) head_project_tile_kernel(const float* __restrict__ x, const float* __restrict__ W, float* __restrict__ out, int T, int H, int n_in, int n_out) {
+    __shared__ float sw[HPT_K][HPT_TILE + 4];
+    __shared__ float sx[HPT_K][HPT_TILE + 4];
+    const int o0 = blockIdx.x * HPT_TILE, t0 = blockIdx.y * HPT_TILE, h = blockIdx.z;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const float* Wh = W + (int64_t)h * n_out * n_in;
+    const int64_t xrs = (int64_t)H * n_in, ors = (int64_t)H * n_out;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
+    for (int k0 = 0; k0 < n_in; k0 += HPT_K) {
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int idx = threadIdx.x + e * 256;
+            const int r = idx >> 4, kk = idx & 15;
+            const bool kin = k0 + kk < n_in;
+            sw[kk][r] = (kin && o0 + r < n_out) ? Wh[(int64_t)(o0 + r) * n_in + k0 + kk] : 0.0f;
+            sx[kk][r] = (kin && t0 + r < T) ? x[(int64_t)(t0 + r) * xrs + h * n_in + k0 + kk] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < HPT_K; kk++) {
+            const float4 wv = *(const float4*)&sw[kk][tx * 4];
+            const float4 xv = *(const float4*)&sx[kk][ty * 4];
+            const float wr[4] = {wv.x, wv.y, wv.z, wv.w}, xr[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(xr[i], wr[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int t = t0 + ty * 4 + i;
+        if (t >= T) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int o = o0 + tx * 4 + j;
+            if (o < n_out) out[(int64_t)t * ors + h * n_out + o] = acc[i][j];
+        }
+    }
+}
 extern "C" CC_API int cc_head_project(cc_device* dev, const cc_view* x, const cc_view* w, int32_t n_heads, int32_t rest, const cc_view* freq, float mag, int64_t pos0,
                                       cc_buf** out) {
     SEQ_ENTER(dev, "head_project");
@@ -1313,6 +1409,12 @@ extern "C" CC_API int cc_head_project(cc_device* dev, const cc_view* x, const cc
     if (rc) return rc;
     *out = o;
     if (T == 0) return CC_OK;
+    if (rest == 0 && T >= 64) {          // a pass of many rows (a prompt): tiles; the sums differ from the few-row kernel's by their order only
+        head_project_tile_kernel<<<dim3((unsigned)((n_out + HPT_TILE - 1) / HPT_TILE), (unsigned)((T + HPT_TILE - 1) / HPT_TILE), (unsigned)n_heads), 256, 0, dev->stream>>>(
+            fptr(x), fptr(w), (float*)o->base, (int)T, n_heads, (int)n_in, (int)n_out);
+        CC_LAUNCH_CHECK(dev);
+        return CC_OK;
+    }
     if (smem > 48 * 1024) CC_CUDA(dev, cudaFuncSetAttribute(head_project_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     head_project_kernel<<<dim3((unsigned)((T + HP_TOK - 1) / HP_TOK), (unsigned)n_heads, (unsigned)((n_out + 3) / 4)), 128, smem, dev->stream>>>(
         fptr(x), fptr(w), (float*)o->base, (int)T, n_heads, (int)n_in, rest, (int)n_out, freq ? fptr(freq) : nullptr, freq ? (int)view_len(freq) : 0, mag, pos0);

@@ -5,8 +5,8 @@
 // Everything is 32-bit (expf / log1pf / expm1f / tanhf of the CUDA math library).  1 - a^2 is taken as -expm1(2 log a): for a decay close to
 // one the difference 1 - a * a would lose most of its digits.
 //
-// Only S ties a token to the one before it, and the tie is one fused multiply-add.  So the work is split: all warps of a CTA turn a block of
-// tokens into the pairs (a, sqrt(1 - a^2) i u) side by side, one warp then walks the block in order, and all warps write the gated
+// Only S ties a token to the one before it, and the tie is one fused multiply-add.  So the work is split: the threads of a CTA turn a block of
+// tokens into the pairs (a, sqrt(1 - a^2) i u) side by side, a few threads then walk the block in order, and all threads write the gated
 // read-outs.  A token's result depends on its inputs and the state alone; the order of the walk is the order of the tokens, whatever the
 // call carries, so prompts, portions and decoding give the same bits.
 #include "../../include/crabml_seqops.h"
@@ -35,9 +35,11 @@ __device__ __forceinline__ float dg_act(float z, int act) {
                                      : z;
 }
 
-#define DG_CH 32            // channels of a CTA: one lane each
-#define DG_WARPS 8
-#define DG_TB 32            // tokens per block
+#define DG_CH 8             // channels of a CTA
+#define DG_ROWS 32          // token rows of the thread layout
+#define DG_PER 4            // tokens per thread and block
+#define DG_TB (DG_ROWS * DG_PER)
+#define DG_THREADS (DG_CH * DG_ROWS)
 struct DgArgs {
     const float *u, *gates, *gate_bias, *lam, *y, *y_bias;
     float *state, *out;
@@ -45,47 +47,69 @@ struct DgArgs {
     int y_act;
     float c;
 };
-// grid ceil(C / 32), 8 warps.  Lane l of every warp is channel blockIdx.x * 32 + l.
-__global__ void __launch_bounds__(DG_CH* DG_WARPS) gated_diag_kernel(DgArgs a) {
+// grid ceil(C / 8), 256 threads, blocks of 128 tokens.  Thread (row, l) = (threadIdx.x / 8, threadIdx.x % 8) is channel blockIdx.x * 8 + l
+// for the block's tokens row, row + 32, row + 64, row + 96 -- four independent chains of exponentials and roots per thread, so that the few
+// warps an SM holds keep its pipes busy; 8 neighbouring channels are one 32-byte sector of every operand row.  The walk over a block's tokens
+// is done by the first 8 threads, one channel each; the operands of its fused multiply-adds are in shared memory and do not depend on S, so
+// the chain is one fmaf per token.
+__global__ void __launch_bounds__(DG_THREADS) gated_diag_kernel(DgArgs a) {
     __shared__ float s_a[DG_TB][DG_CH], s_b[DG_TB][DG_CH], s_s[DG_TB][DG_CH];
-    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    const int ch = blockIdx.x * DG_CH + lane;
+    const int l = threadIdx.x % DG_CH, row = threadIdx.x / DG_CH;
+    const int ch = blockIdx.x * DG_CH + l;
     const bool live = ch < a.C;
-    const int cc = live ? ch : a.C - 1;                       // idle lanes shadow the last channel and never store
+    const int cc = live ? ch : a.C - 1;                       // idle threads shadow the last channel and never store
     const int blk = cc / a.bs, o = cc - blk * a.bs;
     const int col_r = blk * 2 * a.bs + o, col_i = col_r + a.bs;
     const float br = a.gate_bias[col_r], bi = a.gate_bias[col_i];
     const float rate = a.c * dg_softplus(a.lam[cc]);
     const float yb = a.y_bias ? a.y_bias[cc] : 0.0f;
-    float S = w == 0 ? a.state[cc] : 0.0f;
+    float S = row == 0 ? a.state[cc] : 0.0f;
+    // a block's operands are fetched into registers one block ahead: the loads of block n + 1 are in flight while block n is walked and written
+    float g_r[DG_PER], g_i[DG_PER], g_u[DG_PER], g_y[DG_PER];
+    auto fetch = [&](int tb) {
+#pragma unroll
+        for (int e = 0; e < DG_PER; e++) {
+            const int64_t t = tb + row + e * DG_ROWS;
+            const bool in = t < a.T;
+            const float* gr = a.gates + t * 2 * a.C;
+            g_r[e] = in ? gr[col_r] : 0.0f;
+            g_i[e] = in ? gr[col_i] : 0.0f;
+            g_u[e] = in ? a.u[t * a.C + cc] : 0.0f;
+            g_y[e] = (in && a.y) ? a.y[t * a.C + cc] : 0.0f;
+        }
+    };
+    fetch(0);
     for (int tb = 0; tb < a.T; tb += DG_TB) {
         const int nt = min(DG_TB, a.T - tb);
-        for (int tt = w; tt < nt; tt += DG_WARPS) {
-            const int64_t t = tb + tt;
-            const float* gr = a.gates + t * 2 * a.C;
-            const float r = dg_sigmoid(gr[col_r] + br), i = dg_sigmoid(gr[col_i] + bi);
+        float yv[DG_PER];
+#pragma unroll
+        for (int e = 0; e < DG_PER; e++) {
+            const int tt = row + e * DG_ROWS;
+            const float r = dg_sigmoid(g_r[e] + br), i = dg_sigmoid(g_i[e] + bi);
             const float la = -(rate * r);
-            s_a[tt][lane] = expf(la);
-            s_b[tt][lane] = sqrtf(-expm1f(2.0f * la)) * (i * a.u[t * a.C + cc]);
+            s_a[tt][l] = expf(la);
+            s_b[tt][l] = sqrtf(-expm1f(2.0f * la)) * (i * g_u[e]);
+            yv[e] = a.y ? dg_act(g_y[e] + yb, a.y_act) : 1.0f;
         }
+        if (tb + DG_TB < a.T) fetch(tb + DG_TB);
         __syncthreads();
-        if (w == 0) {
+        if (row == 0) {
 #pragma unroll 8
-            for (int tt = 0; tt < nt; tt++) {
-                S = fmaf(s_a[tt][lane], S, s_b[tt][lane]);
-                s_s[tt][lane] = S;
+            for (int k = 0; k < nt; k++) {
+                S = fmaf(s_a[k][l], S, s_b[k][l]);
+                s_s[k][l] = S;
             }
         }
         __syncthreads();
-        if (live)
-            for (int tt = w; tt < nt; tt += DG_WARPS) {
-                const int64_t t = tb + tt;
-                float v = s_s[tt][lane];
-                if (a.y) v *= dg_act(a.y[t * a.C + ch] + yb, a.y_act);
-                a.out[t * a.C + ch] = v;
+        if (live) {
+#pragma unroll
+            for (int e = 0; e < DG_PER; e++) {
+                const int tt = row + e * DG_ROWS;
+                if (tt < nt) a.out[(int64_t)(tb + tt) * a.C + ch] = s_s[tt][l] * yv[e];
             }
+        }
     }
-    if (w == 0 && live) a.state[ch] = S;
+    if (row == 0 && live) a.state[ch] = S;
 }
 
 extern "C" CC_API int cc_gated_diagonal_recurrence(cc_device* dev, const cc_view* u, const cc_view* gates, const cc_view* gate_bias, const cc_view* lam, float c,
@@ -110,7 +134,7 @@ extern "C" CC_API int cc_gated_diagonal_recurrence(cc_device* dev, const cc_view
     DgArgs a{};
     a.u = dptr(u); a.gates = dptr(gates); a.gate_bias = dptr(gate_bias); a.lam = dptr(lam); a.y = y ? dptr(y) : nullptr; a.y_bias = y_bias ? dptr(y_bias) : nullptr;
     a.state = dptr(state); a.out = (float*)o->base; a.T = (int)T; a.C = (int)C; a.bs = (int)(C / n_blocks); a.y_act = y_act; a.c = c;
-    gated_diag_kernel<<<(unsigned)((C + DG_CH - 1) / DG_CH), DG_CH * DG_WARPS, 0, dev->stream>>>(a);
+    gated_diag_kernel<<<(unsigned)((C + DG_CH - 1) / DG_CH), DG_THREADS, 0, dev->stream>>>(a);
     CC_LAUNCH_CHECK(dev);
     return CC_OK;
 }

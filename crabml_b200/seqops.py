@@ -262,3 +262,8 @@ def gated_diagonal_recurrence(u, gates, gate_bias, lam, c, n_blocks, state, y=No
     u.device.check(u.device.lib.cc_gated_diagonal_recurrence(u.device.handle, _v(u), _v(gates), _v(gate_bias), _v(lam), float(c), int(n_blocks), _v(y), _v(y_bias),
                                                              int(y_act), _v(state), C.byref(h)))
     return _new(u.device, h, list(u.shape()))
+
+
+def scaled_sum_accumulate(dst, a, sa, b, sb, c=None):
+    dst.device.check(dst.device.lib.cc_scaled_sum_accumulate(dst.device.handle, _v(dst), _v(a), float(sa), _v(b), float(sb), _v(c)))
+    return dst

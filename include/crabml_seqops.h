@@ -69,6 +69,9 @@ CC_API int cc_glu_halves(cc_device* dev, const cc_view* src, const cc_view* bias
 CC_API int cc_add_row_bias(cc_device* dev, const cc_view* x, const cc_view* bias);
 /* dst = sa * a + sb * b, elementwise (two branches that read one input, joined with fixed weights); dst may be a or b */
 CC_API int cc_scaled_sum(cc_device* dev, const cc_view* dst, const cc_view* a, float sa, const cc_view* b, float sb);
+/* dst += sa * a + sb * b + c, elementwise (c NULL: no third operand): two weighted branches and a third sublayer's result join the residual
+ * stream in one pass. */
+CC_API int cc_scaled_sum_accumulate(cc_device* dev, const cc_view* dst, const cc_view* a, float sa, const cc_view* b, float sb, const cc_view* c);
 /* x[t, h, :] *= act(g[t, h]): ONE gate number per (row, head) on the head's whole output.  x: [rows, heads * head_size], g: [rows, heads]. */
 CC_API int cc_head_gate(cc_device* dev, const cc_view* x, const cc_view* g, int32_t n_heads, int32_t act);
 /* out = [a | b], row by row: a [rows, ca], b [rows, cb] -> out [rows, ca + cb] (two streams that enter one product side by side) */

@@ -71,6 +71,9 @@ def test_head_gate_and_concat(dev):
     assert np.abs(got - x.reshape(9, 5, 7) * R.sigmoid(g)[:, :, None]).max() < 1e-6
     a, b = f32(rng.standard_normal((6, 11))), f32(rng.standard_normal((6, 3)))
     assert np.array_equal(seqops.concat_cols(T32(dev, a), T32(dev, b)).export().reshape(6, 14), np.concatenate([a, b], 1).astype(np.float32))
+    d, e, c = f32(rng.standard_normal((6, 11))), f32(rng.standard_normal((6, 11))), f32(rng.standard_normal((6, 11)))
+    assert np.abs(seqops.scaled_sum_accumulate(T32(dev, a), T32(dev, d), 0.8, T32(dev, e), 1.3, T32(dev, c)).export().reshape(6, 11) - (a + 0.8 * d + 1.3 * e + c)).max() < 1e-6
+    assert np.abs(seqops.scaled_sum_accumulate(T32(dev, a), T32(dev, d), 0.8, T32(dev, e), 1.3).export().reshape(6, 11) - (a + 0.8 * d + 1.3 * e)).max() < 1e-6
     with pytest.raises(TensorError):
         seqops.concat_cols(T32(dev, a), T32(dev, b[:5]))
     with pytest.raises(TensorError):
@@ -273,3 +276,14 @@ def test_convolution_with_bias_without_activation_carries_its_tail(dev):
             tail = zeros(dev, [K - 1, C]) if K > 1 else None
             got = np.concatenate([seqops.short_conv_bias(T32(dev, x[a:b_]), T32(dev, w), T32(dev, b), tail, act=capi.ACT_NONE).export().reshape(b_ - a, C) for a, b_ in cuts(T, sizes)])
             assert np.abs(got - want).max() < 1e-5, (C, K, sizes)
+
+
+@pytest.mark.parametrize("T,H,n_in,n_out", [(64, 3, 8, 16), (200, 2, 70, 33), (130, 1, 128, 256), (7, 2, 20, 9)])
+def test_products_per_block_many_rows_and_few(dev, T, H, n_in, n_out):
+    rng = np.random.default_rng(T)
+    x, w = f32(rng.standard_normal((T, H, n_in))), f32(rng.standard_normal((H, n_out, n_in)))
+    want = np.einsum("thi,hoi->tho", x, w).reshape(T, -1)
+    got = seqops.head_project(T32(dev, x.reshape(T, -1)), T32(dev, w.reshape(H * n_out, n_in)), H).export().reshape(T, -1)
+    assert np.abs(got - want).max() < 1e-4
+    one = seqops.head_project(T32(dev, x[:3].reshape(3, -1)), T32(dev, w.reshape(H * n_out, n_in)), H).export().reshape(3, -1)      # the few-row kernel
+    assert np.abs(one - want[:3]).max() < 1e-4
