@@ -22,6 +22,8 @@ I32, BF16 = 26, 30
 ACT_NONE, ACT_SILU, ACT_GELU_TANH, ACT_SWISH, ACT_SIGMOID = 0, 1, 2, 3, 4
 ROUTE_SOFTMAX, ROUTE_SIGMOID = 0, 1
 ROPE_LLAMA, ROPE_NEOX = 0, 1
+QK_NORM_NONE, QK_NORM_HEAD, QK_NORM_ROW = 0, 1, 2
+ROPE_NEIGHBOURS, ROPE_HALVES = 0, 1
 
 
 class TensorError(Exception):
@@ -272,6 +274,7 @@ def load_library(build_if_missing: bool = True):
         "cc_state_space_scan": (i32, [vp, pv, pv, pv, pv, pv, pv, i32, i32, i32, i32, pp]),
         "cc_layer_norm": (i32, [vp, pv, pv, pv, pv, f32]),
         "cc_head_gate": (i32, [vp, pv, pv, i32, i32]),
+        "cc_qk_prepare_append": (i32, [vp, pv, pv, pv, pv, pv, i32, pv, pv, f32, pv, i32, i32, f32, i64, i32, i32, i32, i32]),
         "cc_scaled_sum_accumulate": (i32, [vp, pv, pv, f32, pv, f32, pv]),
         "cc_concat_cols": (i32, [vp, pv, pv, pp]),
         "cc_rope_halves": (i32, [vp, pv, i32, i32, i32, pv, f32, i64]),

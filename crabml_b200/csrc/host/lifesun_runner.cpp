@@ -5,7 +5,7 @@
 //
 //   pass:   before the first layer of every repetition of the loop: x = W_in [x | x0]
 //   run:    h = LN(x) ; ONE product of everything that multiplies h, cut into its parts ; x += ls * left + rs * right + ff
-//   left:   (q, k norms) ; (rotation) ; keys and values into the run's rings ; masked, capped softmax (+ sink) ; (gate per head) ; W_o
+//   left:   (q, k norms), (rotation) and keys and values into the run's rings, one kernel ; masked, capped softmax (+ sink) ; (gate per head) ; W_o
 //   right:  diagonal: convolution of the x branch ; gates, one product per block ; the recurrence on the run's state, times act(y + b) ; W_o
 //           retention: rotation ; the recurrence on the run's state ; unit RMS per head and silu gate ; W_o
 //   ff:     gelu_tanh(gate) * up ; W_down
@@ -98,23 +98,11 @@ struct Runner : csr_runner {
         const int64_t n = q.shape()[0];
         if (c.window <= 0 && c.block <= 0 && pos0 + n > L.ring)
             throw TensorError("a sequence of " + std::to_string(pos0 + n) + " tokens does not fit the cache of " + std::to_string(L.ring));
-        cc_view qv = q.view(), kv = k.view(), vv = v.view(), tmp{};
-        if (c.qk_norm == CLR_QK_UNIT_PER_HEAD) {
-            check(cc_gated_head_rms_norm(dev, &qv, nullptr, nullptr, c.dim, conf.norm_eps, CC_ACT_NONE));
-            check(cc_gated_head_rms_norm(dev, &kv, nullptr, nullptr, c.dim, conf.norm_eps, CC_ACT_NONE));
-        } else if (c.qk_norm == CLR_QK_WHOLE_WEIGHTED) {
-            cc_view w = L.q_norm.view();
-            check(cc_group_rms_norm(dev, &qv, &qv, &w, 1, conf.norm_eps));
-            w = L.k_norm.view();
-            check(cc_group_rms_norm(dev, &kv, &kv, &w, 1, conf.norm_eps));
-        }
-        if (L.rot_freq.valid()) {
-            cc_view f = L.rot_freq.view();
-            check(cc_rope_halves(dev, &qv, c.heads, c.dim, 0, &f, 1.0f, pos0));
-            check(cc_rope_halves(dev, &kv, c.kv_heads, c.dim, 0, &f, 1.0f, pos0));
-        }
-        cc_view krv = st.kring.view(), vrv = st.vring.view();
-        check(cc_kv_ring_append(dev, &krv, &vrv, &kv, &vv, nullptr, 0.0f, pos0, c.kv_heads, c.dim, c.vdim));
+        cc_view qv = q.view(), kv = k.view(), vv = v.view(), krv = st.kring.view(), vrv = st.vring.view(), tmp{}, qw{}, kw{}, fr{};
+        // norms, rotation and the cache write in one pass
+        const int norm = c.qk_norm == CLR_QK_UNIT_PER_HEAD ? CC_QK_NORM_HEAD : c.qk_norm == CLR_QK_WHOLE_WEIGHTED ? CC_QK_NORM_ROW : CC_QK_NORM_NONE;
+        check(cc_qk_prepare_append(dev, &qv, &kv, &vv, &krv, &vrv, norm, opt(L.q_norm, qw), opt(L.k_norm, kw), conf.norm_eps, opt(L.rot_freq, fr), CC_ROPE_HALVES, 0, 1.0f, pos0,
+                                   c.heads, c.kv_heads, c.dim, c.vdim));
         cc_buf* b = nullptr;
         check(cc_masked_attention_capped(dev, &qv, &krv, &vrv, pos0, c.heads, c.kv_heads, c.dim, c.vdim, c.window, c.block, c.scale, c.softcap, opt(L.sink, tmp), &b));
         CudaTensor o = adopt(b, {n, (int64_t)c.heads * c.vdim});

@@ -1258,6 +1258,122 @@ static int rope_table_impl(cc_device* dev, const cc_view* x, int32_t n_heads, in
     return CC_OK;
 }
 
+// ---- queries and keys from projection to cache in one pass ---------------------------------------------------------------------------------
+struct QkPrepArgs {
+    float *q, *kring, *vring;
+    const float *k, *v, *qw, *kw, *freq;
+    int H, G, dk, dv, ring, norm, half, step, gap, off;      // pair i of a head: columns off + i * step and off + i * step + gap
+    float eps, mag;
+    int64_t pos0;
+};
+#define QKP_THREADS 256
+// one CTA per token.  First the inverse root mean squares -- one per head (a warp per head: lane-strided sum, butterfly) or one per projection
+// (thread-strided sums, butterfly, the warps' sums in warp order) -- then every element once: a rotated pair by the thread of its first
+// column, which reads both raw values and writes both results; all raw values were read for the sums before the barrier, so q may be
+// overwritten in place.
+__global__ void __launch_bounds__(QKP_THREADS) qk_prepare_kernel(QkPrepArgs a) {
+    extern __shared__ float qkp_sm[];               // inv[H + G], red[8]
+    float* inv = qkp_sm;
+    float* red = qkp_sm + a.H + a.G;
+    const int t = blockIdx.x, lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    float* qr = a.q + (int64_t)t * a.H * a.dk;
+    const float* kr = a.k + (int64_t)t * a.G * a.dk;
+    const int units = a.H + a.G;
+    if (a.norm == CC_QK_NORM_HEAD) {
+        for (int u = w; u < units; u += QKP_THREADS / 32) {
+            const float* src = u < a.H ? qr + u * a.dk : kr + (u - a.H) * a.dk;
+            float ss = 0.0f;
+            for (int c = lane; c < a.dk; c += 32) ss = fmaf(src[c], src[c], ss);
+            ss = warp_sum(ss);
+            if (lane == 0) inv[u] = 1.0f / sqrtf(ss / (float)a.dk + a.eps);
+        }
+    } else if (a.norm == CC_QK_NORM_ROW) {
+        for (int side = 0; side < 2; side++) {
+            const float* src = side ? kr : qr;
+            const int n = (side ? a.G : a.H) * a.dk;
+            float ss = 0.0f;
+            for (int c = threadIdx.x; c < n; c += QKP_THREADS) ss = fmaf(src[c], src[c], ss);
+            ss = warp_sum(ss);
+            __syncthreads();
+            if (lane == 0) red[w] = ss;
+            __syncthreads();
+            float tot = 0.0f;
+#pragma unroll
+            for (int i = 0; i < QKP_THREADS / 32; i++) tot += red[i];
+            const float v = 1.0f / sqrtf(tot / (float)n + a.eps);
+            for (int u = threadIdx.x; u < (side ? a.G : a.H); u += QKP_THREADS) inv[(side ? a.H : 0) + u] = v;
+        }
+    } else {
+        for (int u = threadIdx.x; u < units; u += QKP_THREADS) inv[u] = 1.0f;
+    }
+    __syncthreads();
+    const int64_t row = (a.pos0 + t) % a.ring;
+    const float pos = (float)(a.pos0 + t);
+    for (int idx = threadIdx.x; idx < units * a.dk; idx += QKP_THREADS) {
+        const int u = idx / a.dk, c = idx - u * a.dk;
+        const bool is_q = u < a.H;
+        const int ul = is_q ? u : u - a.H;
+        const float* src = is_q ? qr + u * a.dk : kr + ul * a.dk;
+        float* dst = is_q ? qr + u * a.dk : a.kring + (row * a.G + ul) * a.dk;
+        const float* wt = is_q ? a.qw : a.kw;
+        if (wt && a.norm == CC_QK_NORM_ROW) wt += ul * a.dk;
+        const float f = inv[u];
+        const int rel = c - a.off;
+        int pair = -1;                               // index of the pair this thread owns, -2: the pair's second column (its owner writes it)
+        if (rel >= 0 && a.half > 0) {
+            if (a.step == 1) pair = rel < a.half ? rel : rel < 2 * a.half ? -2 : -1;
+            else if (rel < 2 * a.half) pair = (rel & 1) ? -2 : rel >> 1;
+        }
+        if (pair == -2) continue;
+        const float x0 = wt ? src[c] * f * wt[c] : src[c] * f;
+        if (pair >= 0) {
+            const int c1 = c + a.gap;
+            const float x1 = wt ? src[c1] * f * wt[c1] : src[c1] * f;
+            float o0, o1;
+            rotate_pair(x0, x1, pos, a.freq[pair], a.mag, o0, o1);
+            dst[c] = o0; dst[c1] = o1;
+        } else {
+            dst[c] = x0;
+        }
+    }
+    const float* vr = a.v + (int64_t)t * a.G * a.dv;
+    float* vd = a.vring + row * a.G * a.dv;
+    for (int c = threadIdx.x; c < a.G * a.dv; c += QKP_THREADS) vd[c] = vr[c];
+}
+extern "C" CC_API int cc_qk_prepare_append(cc_device* dev, const cc_view* q, const cc_view* k, const cc_view* v, const cc_view* kring, const cc_view* vring, int32_t qk_norm,
+                                           const cc_view* q_w, const cc_view* k_w, float eps, const cc_view* freq, int32_t pairing, int32_t offset, float mag, int64_t pos0,
+                                           int32_t H, int32_t G, int32_t dk, int32_t dv) {
+    SEQ_ENTER(dev, "qk_prepare_append");
+    SEQ_F32(dev, q, "qk_prepare_append q"); SEQ_F32(dev, k, "qk_prepare_append k"); SEQ_F32(dev, v, "qk_prepare_append v");
+    SEQ_F32(dev, kring, "qk_prepare_append kring"); SEQ_F32(dev, vring, "qk_prepare_append vring");
+    CC_REQUIRE(dev, H > 0 && G > 0 && dk > 0 && dv > 0 && q->ndim == 2 && kring->ndim == 2 && pos0 >= 0 && qk_norm >= CC_QK_NORM_NONE && qk_norm <= CC_QK_NORM_ROW,
+               "qk_prepare_append: bad arguments");
+    const int64_t T = q->shape[0], ring = kring->shape[0];
+    CC_REQUIRE(dev, view_len(q) == T * H * dk && view_len(k) == T * G * dk && view_len(v) == T * G * dv && view_len(kring) == ring * G * dk && view_len(vring) == ring * G * dv,
+               "qk_prepare_append: operand sizes do not fit heads=%d kv=%d dk=%d dv=%d", H, G, dk, dv);
+    CC_REQUIRE(dev, T <= ring, "qk_prepare_append: %lld tokens do not fit a ring of %lld", (long long)T, (long long)ring);
+    const int64_t wq = qk_norm == CC_QK_NORM_ROW ? (int64_t)H * dk : dk, wk = qk_norm == CC_QK_NORM_ROW ? (int64_t)G * dk : dk;
+    if (q_w) { SEQ_F32(dev, q_w, "qk_prepare_append q_w"); CC_REQUIRE(dev, qk_norm != CC_QK_NORM_NONE && view_len(q_w) == wq, "qk_prepare_append: q_w must have %lld elements", (long long)wq); }
+    if (k_w) { SEQ_F32(dev, k_w, "qk_prepare_append k_w"); CC_REQUIRE(dev, qk_norm != CC_QK_NORM_NONE && view_len(k_w) == wk, "qk_prepare_append: k_w must have %lld elements", (long long)wk); }
+    int64_t half = 0;
+    if (freq) {
+        SEQ_F32(dev, freq, "qk_prepare_append freq");
+        half = view_len(freq);
+        CC_REQUIRE(dev, offset >= 0 && offset + 2 * half <= dk && (pairing == CC_ROPE_NEIGHBOURS || pairing == CC_ROPE_HALVES), "qk_prepare_append: %lld pairs at column %d do not fit heads of %d",
+                   (long long)half, offset, dk);
+    }
+    if (T == 0) return CC_OK;
+    QkPrepArgs a{};
+    a.q = fptr(q); a.k = fptr(k); a.v = fptr(v); a.kring = fptr(kring); a.vring = fptr(vring); a.qw = q_w ? fptr(q_w) : nullptr; a.kw = k_w ? fptr(k_w) : nullptr;
+    a.freq = freq ? fptr(freq) : nullptr; a.H = H; a.G = G; a.dk = dk; a.dv = dv; a.ring = (int)ring; a.norm = qk_norm; a.half = (int)half; a.off = offset;
+    a.step = pairing == CC_ROPE_HALVES ? 1 : 2; a.gap = pairing == CC_ROPE_HALVES ? (int)half : 1; a.eps = eps; a.mag = mag; a.pos0 = pos0;
+    const size_t smem = (size_t)(H + G + QKP_THREADS / 32) * 4;
+    CC_REQUIRE(dev, smem <= 48 * 1024, "qk_prepare_append: too many heads");
+    qk_prepare_kernel<<<(unsigned)T, QKP_THREADS, smem, dev->stream>>>(a);
+    CC_LAUNCH_CHECK(dev);
+    return CC_OK;
+}
+
 // ---- latent key/value cache ------------------------------------------------------------------------------------------------------------------
 // one warp per token: the first `rank` columns are RMS-normalised and weighted, the pairs of the next columns rotated, the rest copied
 __global__ void latent_ring_append_kernel(float* __restrict__ ring, const float* __restrict__ ckv, const float* __restrict__ nw, const float* __restrict__ freq, float eps,

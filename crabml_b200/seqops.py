@@ -267,3 +267,11 @@ def gated_diagonal_recurrence(u, gates, gate_bias, lam, c, n_blocks, state, y=No
 def scaled_sum_accumulate(dst, a, sa, b, sb, c=None):
     dst.device.check(dst.device.lib.cc_scaled_sum_accumulate(dst.device.handle, _v(dst), _v(a), float(sa), _v(b), float(sb), _v(c)))
     return dst
+
+
+def qk_prepare_append(q, k, v, kring, vring, pos0, n_heads, n_kv, dk, dv, qk_norm=capi.QK_NORM_NONE, q_w=None, k_w=None, eps=0.0, freq=None, pairing=capi.ROPE_HALVES, offset=0,
+                      mag=1.0):
+    """norms, rotation and the cache write between the projections and the attention, one kernel; q is overwritten"""
+    q.device.check(q.device.lib.cc_qk_prepare_append(q.device.handle, _v(q), _v(k), _v(v), _v(kring), _v(vring), int(qk_norm), _v(q_w), _v(k_w), float(eps), _v(freq), int(pairing),
+                                                     int(offset), float(mag), int(pos0), n_heads, n_kv, dk, dv))
+    return q

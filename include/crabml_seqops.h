@@ -188,6 +188,20 @@ CC_API int cc_rope_pairs(cc_device* dev, const cc_view* x, int32_t n_heads, int3
  * "two halves" layout; all other columns stay.  In place. */
 CC_API int cc_rope_halves(cc_device* dev, const cc_view* x, int32_t n_heads, int32_t head_size, int32_t offset, const cc_view* freq, float mag, int64_t pos0);
 
+/* ---- queries and keys from projection to cache in one pass ------------------------------------------------------------------------ */
+/* What lies between the projections and the attention, fused: q [T, n_heads * dk] and k [T, n_kv * dk] are normalised, rotated, q is
+ * written back in place, k and v [T, n_kv * dv] go into the rings' rows of positions pos0 .. (cc_kv_ring_append's layout).
+ *   qk_norm  CC_QK_NORM_NONE; CC_QK_NORM_HEAD: every head divided by sqrt(mean(head^2) + eps), times q_w / k_w [dk] (NULL: 1);
+ *            CC_QK_NORM_ROW: the whole projection divided by sqrt(mean(row^2) + eps), times q_w [n_heads * dk] / k_w [n_kv * dk] (NULL: 1)
+ *   freq     [P] or NULL: after the norm, P column pairs of every head starting at column `offset` turn by position * freq[i], times mag;
+ *            pairing CC_ROPE_NEIGHBOURS: (offset + 2i, offset + 2i + 1), CC_ROPE_HALVES: (offset + i, offset + i + P)
+ * The same arithmetic as cc_gated_head_rms_norm / cc_group_rms_norm, cc_rope_pairs / cc_rope_halves and cc_kv_ring_append one after the other. */
+enum cc_qk_norm { CC_QK_NORM_NONE = 0, CC_QK_NORM_HEAD = 1, CC_QK_NORM_ROW = 2 };
+enum cc_rope_pairing { CC_ROPE_NEIGHBOURS = 0, CC_ROPE_HALVES = 1 };
+CC_API int cc_qk_prepare_append(cc_device* dev, const cc_view* q, const cc_view* k, const cc_view* v, const cc_view* kring, const cc_view* vring, int32_t qk_norm,
+                                const cc_view* q_w, const cc_view* k_w, float eps, const cc_view* freq, int32_t pairing, int32_t offset, float mag, int64_t pos0,
+                                int32_t n_heads, int32_t n_kv, int32_t dk, int32_t dv);
+
 /* ---- latent key/value cache --------------------------------------------------------------------------------------------------- */
 /* A cache row is [c | r]: c, `rank` numbers from which keys and values of all heads derive, and r, a rotated key part that all heads
  * share.  Appends T rows ckv [T, cols] at positions pos0 .. to ring [R, cols] (position p lives in row p % R): the first `rank` columns

@@ -287,3 +287,41 @@ def test_products_per_block_many_rows_and_few(dev, T, H, n_in, n_out):
     assert np.abs(got - want).max() < 1e-4
     one = seqops.head_project(T32(dev, x[:3].reshape(3, -1)), T32(dev, w.reshape(H * n_out, n_in)), H).export().reshape(3, -1)      # the few-row kernel
     assert np.abs(one - want[:3]).max() < 1e-4
+
+
+@pytest.mark.parametrize("norm", ["none", "head", "row"])
+@pytest.mark.parametrize("pairing,dims,offset", [("halves", 6, 0), ("halves", 10, 0), ("neighbours", 4, 2), (None, 0, 0)])
+def test_norms_rotation_and_cache_write_in_one_pass(dev, norm, pairing, dims, offset):
+    """against the reference's steps one after the other; the ring wraps, and rows of other positions stay as they were"""
+    rng = np.random.default_rng(dims + len(norm))
+    T, H, G, dk, dv, ring, pos0, eps = 9, 3, 2, 10, 7, 12, 20, 1e-3
+    q, k, v = f32(rng.standard_normal((T, H, dk)) * 2), f32(rng.standard_normal((T, G, dk)) * 2), f32(rng.standard_normal((T, G, dv)))
+    qw = f32(1 + 0.3 * rng.standard_normal(H * dk if norm == "row" else dk))
+    kw = f32(1 + 0.3 * rng.standard_normal(G * dk if norm == "row" else dk))
+    if norm == "head":
+        wq, wk = R.unit_rms(q, eps) * qw, R.unit_rms(k, eps) * kw
+    elif norm == "row":
+        wq, wk = (R.unit_rms(q.reshape(T, -1), eps) * qw).reshape(T, H, dk), (R.unit_rms(k.reshape(T, -1), eps) * kw).reshape(T, G, dk)
+    else:
+        wq, wk = q.copy(), k.copy()
+    f = None
+    if pairing:
+        base, pos = 50.0, np.arange(pos0, pos0 + T)
+        f = T32(dev, (base ** (-2.0 * np.arange(dims // 2) / dims)).astype(np.float32))
+        if pairing == "halves":
+            wq, wk = R.rotate_half(wq, pos, dims, base), R.rotate_half(wk, pos, dims, base)
+        else:                                                   # neighbouring columns from `offset` on: the half layout of the reordered columns
+            order = [offset + 2 * i for i in range(dims // 2)] + [offset + 2 * i + 1 for i in range(dims // 2)]
+            for w_ in (wq, wk):
+                w_[..., order] = R.rotate_half(w_[..., order], pos, dims, base)
+    kr, vr = T32(dev, np.full((ring, G * dk), 7.0)), T32(dev, np.full((ring, G * dv), 7.0))
+    tq = T32(dev, q.reshape(T, -1))
+    seqops.qk_prepare_append(tq, T32(dev, k.reshape(T, -1)), T32(dev, v.reshape(T, -1)), kr, vr, pos0, H, G, dk, dv,
+                             qk_norm={"none": capi.QK_NORM_NONE, "head": capi.QK_NORM_HEAD, "row": capi.QK_NORM_ROW}[norm], q_w=None if norm == "none" else T32(dev, qw),
+                             k_w=None if norm == "none" else T32(dev, kw), eps=eps, freq=f, pairing=capi.ROPE_NEIGHBOURS if pairing == "neighbours" else capi.ROPE_HALVES, offset=offset)
+    assert np.abs(tq.export().reshape(T, H, dk) - wq).max() < 2e-5
+    gk, gv = kr.export().reshape(ring, G, dk), vr.export().reshape(ring, G, dv)
+    rows = [(pos0 + t) % ring for t in range(T)]
+    assert np.abs(gk[rows] - wk).max() < 2e-5 and np.array_equal(gv[rows], v.astype(np.float32))
+    others = [r for r in range(ring) if r not in rows]
+    assert np.all(gk[others] == 7.0) and np.all(gv[others] == 7.0)
