@@ -274,6 +274,8 @@ def load_library(build_if_missing: bool = True):
         "cc_state_space_scan": (i32, [vp, pv, pv, pv, pv, pv, pv, i32, i32, i32, i32, pp]),
         "cc_layer_norm": (i32, [vp, pv, pv, pv, pv, f32]),
         "cc_head_gate": (i32, [vp, pv, pv, i32, i32]),
+        "cc_rope_halves_two": (i32, [vp, pv, pv, i32, i32, i32, pv, f32, i64]),
+        "cc_short_conv_biases": (i32, [vp, pv, pv, pv, pv, pv, i32, pp]),
         "cc_qk_prepare_append": (i32, [vp, pv, pv, pv, pv, pv, i32, pv, pv, f32, pv, i32, i32, f32, i64, i32, i32, i32, i32]),
         "cc_scaled_sum_accumulate": (i32, [vp, pv, pv, f32, pv, f32, pv]),
         "cc_concat_cols": (i32, [vp, pv, pv, pp]),

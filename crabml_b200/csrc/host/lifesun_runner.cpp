@@ -117,10 +117,10 @@ struct Runner : csr_runner {
         const auto& c = L.c;
         const int64_t n = part[0].shape()[0];
         CudaTensor &y = part[L.i_right], &xb = part[L.i_right + 1];
-        cc_view xv = xb.view(), cw = L.conv.view(), cb{}, tl{};
-        if (L.x_bias.valid()) { cc_view bv = L.x_bias.view(); check(cc_add_row_bias(dev, &xv, &bv)); }      // the projection's bias comes before the convolution
+        cc_view xv = xb.view(), cw = L.conv.view(), cb{}, tl{}, ib{};
         cc_buf* b = nullptr;
-        check(cc_short_conv_bias(dev, &xv, &cw, opt(L.conv_bias, cb), opt(st.tail, tl), CC_ACT_NONE, &b));
+        // the projection's bias comes before the convolution: the kernel adds it to the inputs it reads
+        check(cc_short_conv_biases(dev, &xv, &cw, opt(L.x_bias, ib), opt(L.conv_bias, cb), opt(st.tail, tl), CC_ACT_NONE, &b));
         CudaTensor u = adopt(b, {n, c.r_width});
         b = nullptr;
         cc_view uv = u.view(), gw = L.gate_w.view();
@@ -139,8 +139,7 @@ struct Runner : csr_runner {
         cc_view rq = part[r0].view(), rk = part[r0 + 1].view(), rv = part[r0 + 2].view(), rg = part[r0 + 3].view(), sv = st.S.view(), dv = L.decay.view();
         if (L.r_rot_freq.valid()) {
             cc_view f = L.r_rot_freq.view();
-            check(cc_rope_halves(dev, &rq, c.r_heads, c.r_dim, 0, &f, 1.0f, pos0));
-            check(cc_rope_halves(dev, &rk, c.r_heads, c.r_dim, 0, &f, 1.0f, pos0));
+            check(cc_rope_halves_two(dev, &rq, &rk, c.r_heads, c.r_dim, 0, &f, 1.0f, pos0));
         }
         cc_buf* b = nullptr;
         check(cc_retention(dev, &rq, &rk, &rv, &dv, 1.0f / std::sqrt((float)c.r_dim), &sv, c.r_heads, c.r_dim, c.r_vdim, &b));

@@ -298,8 +298,9 @@ extern "C" CC_API int cc_pair_hash_rows_add(cc_device* dev, const cc_view* dst, 
 
 // ---- short causal convolution ----------------------------------------------------------------------------------------------------
 // one warp per (token, run of hs channels).  in[t'] for t' < 0 comes from the tail: tail row (K-1) + t'.
+// in_bias (or NULL) is added to every input of x as it is read; the tail holds inputs that already carry it (or the zeros before a sequence)
 __global__ void short_conv_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias, const float* __restrict__ tail,
-                                  float* __restrict__ y, int T, int C, int K, int hs, int act, int unit, float ueps, float uscale) {
+                                  float* __restrict__ y, int T, int C, int K, int hs, int act, int unit, float ueps, float uscale, const float* __restrict__ in_bias) {
     const int heads = C / hs;
     const int64_t u = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
@@ -311,7 +312,7 @@ __global__ void short_conv_kernel(const float* __restrict__ x, const float* __re
         float acc = bias ? bias[c] : 0.0f;
         for (int j = 0; j < K; j++) {
             const int ti = t - (K - 1) + j;
-            const float v = ti >= 0 ? x[(int64_t)ti * C + c] : tail[(int64_t)(ti + K - 1) * C + c];
+            const float v = ti >= 0 ? (in_bias ? x[(int64_t)ti * C + c] + in_bias[c] : x[(int64_t)ti * C + c]) : tail[(int64_t)(ti + K - 1) * C + c];
             acc = fmaf(w[(int64_t)c * K + j], v, acc);
         }
         acc = seq_act(acc, act);
@@ -325,16 +326,17 @@ __global__ void short_conv_kernel(const float* __restrict__ x, const float* __re
     }
 }
 // tail <- the last K-1 rows of (tail ++ x); one thread per channel, ascending rows: row j is written after row T + j > j was read
-__global__ void short_conv_tail_kernel(const float* __restrict__ x, float* __restrict__ tail, int T, int C, int K) {
+__global__ void short_conv_tail_kernel(const float* __restrict__ x, float* __restrict__ tail, int T, int C, int K, const float* __restrict__ in_bias) {
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= C) return;
+    const float ib = in_bias ? in_bias[c] : 0.0f;
     for (int j = 0; j < K - 1; j++) {
         const int ti = T + j - (K - 1);
-        tail[(int64_t)j * C + c] = ti >= 0 ? x[(int64_t)ti * C + c] : tail[(int64_t)(ti + K - 1) * C + c];
+        tail[(int64_t)j * C + c] = ti >= 0 ? (in_bias ? x[(int64_t)ti * C + c] + ib : x[(int64_t)ti * C + c]) : tail[(int64_t)(ti + K - 1) * C + c];
     }
 }
 static int short_conv_impl(cc_device* dev, const cc_view* x, const cc_view* w, const cc_view* bias, const cc_view* tail, int32_t act, int32_t head_size, int32_t unit_norm,
-                           float unit_eps, float unit_scale, cc_buf** out) {
+                           float unit_eps, float unit_scale, cc_buf** out, const cc_view* in_bias = nullptr) {
     SEQ_ENTER(dev, "short_conv");
     if (!out) return cc_fail(dev, CC_ERR_ARG, "short_conv: out is NULL");
     SEQ_F32(dev, x, "short_conv x"); SEQ_F32(dev, w, "short_conv w");
@@ -352,6 +354,8 @@ static int short_conv_impl(cc_device* dev, const cc_view* x, const cc_view* w, c
         while (C % hs) hs--;
     }
     if (bias) { SEQ_F32(dev, bias, "short_conv bias"); CC_REQUIRE(dev, view_len(bias) == C, "short_conv: the bias needs one number per channel"); }
+    if (in_bias) { SEQ_F32(dev, in_bias, "short_conv in_bias"); CC_REQUIRE(dev, view_len(in_bias) == C, "short_conv: the input bias needs one number per channel"); }
+    const float* ibp = in_bias ? fptr(in_bias) : nullptr;
     cc_buf* y = nullptr;
     int rc = cc_new_activation(dev, T * C, CC_F32, false, &y);
     if (rc) return rc;
@@ -360,10 +364,10 @@ static int short_conv_impl(cc_device* dev, const cc_view* x, const cc_view* w, c
     const float* tp = K > 1 ? fptr(tail) : nullptr;
     const int64_t units = T * (C / hs);
     short_conv_kernel<<<(unsigned)((units + 7) / 8), 256, 0, dev->stream>>>(fptr(x), fptr(w), bias ? fptr(bias) : nullptr, tp, (float*)y->base, (int)T, (int)C, (int)K, hs, act, unit_norm,
-                                                                        unit_eps, unit_scale);
+                                                                        unit_eps, unit_scale, ibp);
     CC_LAUNCH_CHECK(dev);
     if (K > 1) {
-        short_conv_tail_kernel<<<(unsigned)((C + 127) / 128), 128, 0, dev->stream>>>(fptr(x), fptr(tail), (int)T, (int)C, (int)K);
+        short_conv_tail_kernel<<<(unsigned)((C + 127) / 128), 128, 0, dev->stream>>>(fptr(x), fptr(tail), (int)T, (int)C, (int)K, ibp);
         CC_LAUNCH_CHECK(dev);
     }
     return CC_OK;
@@ -372,6 +376,10 @@ static int short_conv_impl(cc_device* dev, const cc_view* x, const cc_view* w, c
 extern "C" CC_API int cc_short_conv(cc_device* dev, const cc_view* x, const cc_view* w, const cc_view* tail, int32_t act, int32_t head_size, int32_t unit_norm,
                                     float unit_eps, float unit_scale, cc_buf** out) {
     return short_conv_impl(dev, x, w, nullptr, tail, act, head_size, unit_norm, unit_eps, unit_scale, out);
+}
+extern "C" CC_API int cc_short_conv_biases(cc_device* dev, const cc_view* x, const cc_view* w, const cc_view* in_bias, const cc_view* bias, const cc_view* tail, int32_t act,
+                                           cc_buf** out) {
+    return short_conv_impl(dev, x, w, bias, tail, act, 0, 0, 0.0f, 1.0f, out, in_bias);
 }
 extern "C" CC_API int cc_short_conv_bias(cc_device* dev, const cc_view* x, const cc_view* w, const cc_view* bias, const cc_view* tail, int32_t act, cc_buf** out) {
     return short_conv_impl(dev, x, w, bias, tail, act, 0, 0, 0.0f, 1.0f, out);
@@ -1226,10 +1234,11 @@ __device__ __forceinline__ void rotate_pair(float u, float v, float pos, float f
 // one thread per (token, head, pair)
 // pair i of a head is the columns off + i * step and off + i * step + gap: (step, gap) = (2, 1) pairs neighbours, (1, half) pairs the two
 // halves of the rotated columns
-__global__ void rope_pairs_kernel(float* __restrict__ x, const float* __restrict__ freq, int64_t n, int heads, int hs, int off, int half, float mag, int64_t pos0, int step,
-                                  int gap) {
-    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= n) return;
+__global__ void rope_pairs_kernel(float* x, const float* __restrict__ freq, int64_t n, int heads, int hs, int off, int half, float mag, int64_t pos0, int step, int gap,
+                                  float* x2) {
+    int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (x2 ? 2 * n : n)) return;
+    if (idx >= n) { idx -= n; x = x2; }                              // a second tensor of the same shape rides along
     const int i = (int)(idx % half);
     const int64_t th = idx / half;                                   // token * heads + head
     float* p = x + th * hs + off + step * i;
@@ -1237,23 +1246,32 @@ __global__ void rope_pairs_kernel(float* __restrict__ x, const float* __restrict
     rotate_pair(p[0], p[gap], (float)(pos0 + th / heads), freq[i], mag, ou, ov);
     p[0] = ou; p[gap] = ov;
 }
-static int rope_table_impl(cc_device* dev, const cc_view* x, int32_t n_heads, int32_t head_size, int32_t offset, const cc_view* freq, float mag, int64_t pos0, bool halves);
+static int rope_table_impl(cc_device* dev, const cc_view* x, int32_t n_heads, int32_t head_size, int32_t offset, const cc_view* freq, float mag, int64_t pos0, bool halves,
+                           const cc_view* x2 = nullptr);
 extern "C" CC_API int cc_rope_pairs(cc_device* dev, const cc_view* x, int32_t n_heads, int32_t head_size, int32_t offset, const cc_view* freq, float mag, int64_t pos0) {
     return rope_table_impl(dev, x, n_heads, head_size, offset, freq, mag, pos0, false);
 }
 extern "C" CC_API int cc_rope_halves(cc_device* dev, const cc_view* x, int32_t n_heads, int32_t head_size, int32_t offset, const cc_view* freq, float mag, int64_t pos0) {
     return rope_table_impl(dev, x, n_heads, head_size, offset, freq, mag, pos0, true);
 }
-static int rope_table_impl(cc_device* dev, const cc_view* x, int32_t n_heads, int32_t head_size, int32_t offset, const cc_view* freq, float mag, int64_t pos0, bool halves) {
+extern "C" CC_API int cc_rope_halves_two(cc_device* dev, const cc_view* x1, const cc_view* x2, int32_t n_heads, int32_t head_size, int32_t offset, const cc_view* freq, float mag,
+                                         int64_t pos0) {
+    if (dev && !x2) return cc_fail(dev, CC_ERR_ARG, "rope_halves_two: the second tensor is NULL");
+    return rope_table_impl(dev, x1, n_heads, head_size, offset, freq, mag, pos0, true, x2);
+}
+static int rope_table_impl(cc_device* dev, const cc_view* x, int32_t n_heads, int32_t head_size, int32_t offset, const cc_view* freq, float mag, int64_t pos0, bool halves,
+                           const cc_view* x2) {
     SEQ_ENTER(dev, "rope_pairs");
+    if (x2) { SEQ_F32(dev, x2, "rope_pairs second tensor"); CC_REQUIRE(dev, x2->ndim == 2 && x->ndim == 2 && x2->shape[0] == x->shape[0] && x2->shape[1] == x->shape[1], "rope_pairs: the two tensors differ in shape"); }
     SEQ_F32(dev, x, "rope_pairs x"); SEQ_F32(dev, freq, "rope_pairs freq");
     const int64_t half = view_len(freq);
     CC_REQUIRE(dev, x->ndim == 2 && n_heads > 0 && head_size > 0 && x->shape[1] == (int64_t)n_heads * head_size && offset >= 0 && offset + 2 * half <= head_size && pos0 >= 0,
                "rope_pairs: %lld pairs at column %d do not fit heads of %d", (long long)half, offset, head_size);
     const int64_t n = x->shape[0] * n_heads * half;
     if (n == 0) return CC_OK;
-    rope_pairs_kernel<<<(unsigned)((n + 255) / 256), 256, 0, dev->stream>>>(fptr(x), fptr(freq), n, n_heads, head_size, offset, (int)half, mag, pos0, halves ? 1 : 2,
-                                                                            halves ? (int)half : 1);
+    const int64_t items = x2 ? 2 * n : n;
+    rope_pairs_kernel<<<(unsigned)((items + 255) / 256), 256, 0, dev->stream>>>(fptr(x), fptr(freq), n, n_heads, head_size, offset, (int)half, mag, pos0, halves ? 1 : 2,
+                                                                                halves ? (int)half : 1, x2 ? fptr(x2) : nullptr);
     CC_LAUNCH_CHECK(dev);
     return CC_OK;
 }

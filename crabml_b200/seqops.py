@@ -275,3 +275,15 @@ def qk_prepare_append(q, k, v, kring, vring, pos0, n_heads, n_kv, dk, dv, qk_nor
     q.device.check(q.device.lib.cc_qk_prepare_append(q.device.handle, _v(q), _v(k), _v(v), _v(kring), _v(vring), int(qk_norm), _v(q_w), _v(k_w), float(eps), _v(freq), int(pairing),
                                                      int(offset), float(mag), int(pos0), n_heads, n_kv, dk, dv))
     return q
+
+
+def rope_halves_two(x1, x2, n_heads, head_size, offset, freq, mag, pos0):
+    x1.device.check(x1.device.lib.cc_rope_halves_two(x1.device.handle, _v(x1), _v(x2), int(n_heads), int(head_size), int(offset), _v(freq), float(mag), int(pos0)))
+    return x1, x2
+
+
+def short_conv_biases(x, w, in_bias, bias, tail, act=capi.ACT_NONE):
+    """the convolution over x + in_bias (zeros before the sequence), plus bias, then the activation"""
+    h = C.c_void_p()
+    x.device.check(x.device.lib.cc_short_conv_biases(x.device.handle, _v(x), _v(w), _v(in_bias), _v(bias), _v(tail), int(act), C.byref(h)))
+    return _new(x.device, h, x.shape())

@@ -93,6 +93,10 @@ CC_API int cc_pair_hash_rows_add(cc_device* dev, const cc_view* dst, const cc_vi
 CC_API int cc_short_conv(cc_device* dev, const cc_view* x, const cc_view* w, const cc_view* tail, int32_t act, int32_t head_size,
                          int32_t unit_norm, float unit_eps, float unit_scale, cc_buf** out);
 
+/* cc_short_conv_bias with a bias on the INPUT as well (in_bias: [C] or NULL): the convolution runs over x + in_bias -- the bias of the projection
+ * that made x -- while the positions before the sequence stay zero; the tail then holds inputs that carry the bias. */
+CC_API int cc_short_conv_biases(cc_device* dev, const cc_view* x, const cc_view* w, const cc_view* in_bias, const cc_view* bias, const cc_view* tail, int32_t act,
+                                cc_buf** out);
 /* cc_short_conv with a bias per channel added to the sum before the activation (bias: [C] or NULL) */
 CC_API int cc_short_conv_bias(cc_device* dev, const cc_view* x, const cc_view* w, const cc_view* bias, const cc_view* tail, int32_t act, cc_buf** out);
 
@@ -187,6 +191,9 @@ CC_API int cc_rope_pairs(cc_device* dev, const cc_view* x, int32_t n_heads, int3
 /* The same rotation with another pairing: with P = len(freq), column offset + i turns together with column offset + i + P (i < P), the
  * "two halves" layout; all other columns stay.  In place. */
 CC_API int cc_rope_halves(cc_device* dev, const cc_view* x, int32_t n_heads, int32_t head_size, int32_t offset, const cc_view* freq, float mag, int64_t pos0);
+/* cc_rope_halves on two tensors of one shape (the queries and keys of a mixer whose heads are equally many) in one pass */
+CC_API int cc_rope_halves_two(cc_device* dev, const cc_view* x1, const cc_view* x2, int32_t n_heads, int32_t head_size, int32_t offset, const cc_view* freq, float mag,
+                              int64_t pos0);
 
 /* ---- queries and keys from projection to cache in one pass ------------------------------------------------------------------------ */
 /* What lies between the projections and the attention, fused: q [T, n_heads * dk] and k [T, n_kv * dk] are normalised, rotated, q is

@@ -91,6 +91,11 @@ def test_rotation_of_half_pairs(dev, heads, hs, dims, base):
     # rows 5 .. as positions 5 ..: a portion of a prompt
     got = seqops.rope_halves(T32(dev, x[5:]), heads, hs, 0, f, 1.0, 5).export().reshape(7, -1)
     assert np.abs(got - want[5:]).max() < 2e-5
+    # two tensors in one pass
+    x2 = f32(rng.standard_normal((12, heads * hs)))
+    a, b = seqops.rope_halves_two(T32(dev, x), T32(dev, x2), heads, hs, 0, f, 1.0, 0)
+    assert np.abs(a.export().reshape(12, -1) - want).max() < 2e-5
+    assert np.abs(b.export().reshape(12, -1) - R.rotate_half(x2.reshape(12, heads, hs), np.arange(12), dims, base).reshape(12, -1)).max() < 2e-5
     # far positions: the angle is a 32-bit product, so compare against the reference fed that product
     far = np.array([100000 + i for i in range(12)])
     ang = (far[:, None].astype(np.float32) * f.export()[None, :].astype(np.float32)).astype(np.float64)
@@ -276,6 +281,11 @@ def test_convolution_with_bias_without_activation_carries_its_tail(dev):
             tail = zeros(dev, [K - 1, C]) if K > 1 else None
             got = np.concatenate([seqops.short_conv_bias(T32(dev, x[a:b_]), T32(dev, w), T32(dev, b), tail, act=capi.ACT_NONE).export().reshape(b_ - a, C) for a, b_ in cuts(T, sizes)])
             assert np.abs(got - want).max() < 1e-5, (C, K, sizes)
+            # the bias of the projection that made x, added inside: zeros before the sequence stay zeros
+            xb = f32(rng.standard_normal(C))
+            tail = zeros(dev, [K - 1, C]) if K > 1 else None
+            got = np.concatenate([seqops.short_conv_biases(T32(dev, x[a:b_]), T32(dev, w), T32(dev, xb), T32(dev, b), tail).export().reshape(b_ - a, C) for a, b_ in cuts(T, sizes)])
+            assert np.abs(got - R.causal_conv(x + xb, w, b)).max() < 1e-5, (C, K, sizes)
 
 
 @pytest.mark.parametrize("T,H,n_in,n_out", [(64, 3, 8, 16), (200, 2, 70, 33), (130, 1, 128, 256), (7, 2, 20, 9)])
