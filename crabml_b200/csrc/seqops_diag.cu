@@ -35,9 +35,10 @@ __device__ __forceinline__ float dg_act(float z, int act) {
                                      : z;
 }
 
-#define DG_CH 8             // channels of a CTA
-#define DG_ROWS 32          // token rows of the thread layout
-#define DG_PER 4            // tokens per thread and block
+#define DG_CH 4             // channels of a CTA
+#define DG_ROWS 64          // token rows of the thread layout
+#define DG_PER 2            // tokens per thread and block
+#define DG_WALK 16          // tokens whose operands the walk keeps in registers at a time
 #define DG_TB (DG_ROWS * DG_PER)
 #define DG_THREADS (DG_CH * DG_ROWS)
 struct DgArgs {
@@ -47,11 +48,10 @@ struct DgArgs {
     int y_act;
     float c;
 };
-// grid ceil(C / 8), 256 threads, blocks of 128 tokens.  Thread (row, l) = (threadIdx.x / 8, threadIdx.x % 8) is channel blockIdx.x * 8 + l
-// for the block's tokens row, row + 32, row + 64, row + 96 -- four independent chains of exponentials and roots per thread, so that the few
-// warps an SM holds keep its pipes busy; 8 neighbouring channels are one 32-byte sector of every operand row.  The walk over a block's tokens
-// is done by the first 8 threads, one channel each; the operands of its fused multiply-adds are in shared memory and do not depend on S, so
-// the chain is one fmaf per token.
+// grid ceil(C / 4), 256 threads, blocks of 128 tokens.  Thread (row, l) = (threadIdx.x / 4, threadIdx.x % 4) is channel blockIdx.x * 4 + l
+// for the block's tokens row and row + 64 -- independent chains of exponentials and roots; an SM holds two such CTAs, so that one computes
+// gates while the other walks.  The walk over a block's tokens is done by the first 4 threads, one channel each: the operands of 16 tokens are
+// read from shared memory into registers at once (they do not depend on S), then the chain is one fmaf per token.
 __global__ void __launch_bounds__(DG_THREADS) gated_diag_kernel(DgArgs a) {
     __shared__ float s_a[DG_TB][DG_CH], s_b[DG_TB][DG_CH], s_s[DG_TB][DG_CH];
     const int l = threadIdx.x % DG_CH, row = threadIdx.x / DG_CH;
@@ -94,10 +94,16 @@ __global__ void __launch_bounds__(DG_THREADS) gated_diag_kernel(DgArgs a) {
         if (tb + DG_TB < a.T) fetch(tb + DG_TB);
         __syncthreads();
         if (row == 0) {
-#pragma unroll 8
-            for (int k = 0; k < nt; k++) {
-                S = fmaf(s_a[k][l], S, s_b[k][l]);
-                s_s[k][l] = S;
+            for (int k0 = 0; k0 < nt; k0 += DG_WALK) {
+                float av[DG_WALK], bv[DG_WALK];
+#pragma unroll
+                for (int j = 0; j < DG_WALK; j++) { av[j] = s_a[k0 + j][l]; bv[j] = s_b[k0 + j][l]; }
+#pragma unroll
+                for (int j = 0; j < DG_WALK; j++) {
+                    const float next = fmaf(av[j], S, bv[j]);
+                    S = k0 + j < nt ? next : S;              // rows behind the last token hold values made from zeros: they are not applied
+                    s_s[k0 + j][l] = S;
+                }
             }
         }
         __syncthreads();
