@@ -7,7 +7,7 @@ def dense(ff=40):
     return {"kind": "dense", "ff": ff}
 
 
-def lru_layer(block=7, mlp="default", heads=6, kv_heads=2, dim=10, vdim=6, scale=0.6, width=24, blocks=3, conv=4, ls=1.2, rs=0.8):
+def lru_layer(block=7, mlp="default", heads=6, kv_heads=2, dim=10, vdim=6, scale=0.6, width=24, blocks=3, conv=4, ls=1.25, rs=0.75):
     """attention without positions in blocks of positions, unit-RMS queries and keys, one more 1 in the denominator, a gate per head; beside
     the gated diagonal recurrence"""
     return {"type": "parallel", "mlp": dense() if mlp == "default" else mlp,
@@ -16,7 +16,7 @@ def lru_layer(block=7, mlp="default", heads=6, kv_heads=2, dim=10, vdim=6, scale
 
 
 def retention_layer(window=5, mlp="default", heads=4, kv_heads=2, dim=12, vdim=8, scale=0.4, rot=(6, 100.0), softcap=3.0, r_heads=3, r_dim=8, r_vdim=10,
-                    decay=(0.9, 0.97, 0.6), r_rot=(8, 1000.0), ls=0.9, rs=1.3):
+                    decay=(0.9, 0.97, 0.6), r_rot=(8, 1000.0), ls=0.85, rs=1.3):
     """windowed attention with whole-projection norms, half-paired rotation and capped scores; beside retention"""
     left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale, "mask": {"size": window}}
     if rot:

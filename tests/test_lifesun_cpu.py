@@ -60,7 +60,7 @@ def test_rotation_pairs_column_i_with_i_plus_half_and_leaves_the_rest():
 
 
 def test_frequency_table_of_the_package_is_the_reference_rule():
-    for dims, base in ((2, 10.0), (6, 100.0), (64, 3e6), (48, 2e5)):
+    for dims, base in ((2, 10.0), (6, 100.0), (64, 3e6), (40, 2e5)):
         f, mag = rotary.table_of({"dims": dims, "base": base})
         assert mag == 1.0 and f.dtype == np.float32 and len(f) == dims // 2
         assert np.allclose(f, float(base) ** (-2.0 * np.arange(dims // 2) / dims), rtol=1e-7)
