@@ -48,6 +48,7 @@ WORKLOADS = {
     # the Lifesun family at the same layer sizes, beside the Vuzinex stack of equal width and depth; see run_lifesun
     "lifesun-w1024": ("LIFESUN", "BF16", "BF16"),
     "lifesun-w2048": ("LIFESUN", "BF16", "BF16"),
+    "lifesun-w4096": ("LIFESUN", "BF16", "BF16"),
 }
 # dram bytes per megakernel launch from the committed ncu --set full capture (profiles/); None until captured
 TRAFFIC = {("llama2-7b-q8_0", 1): 7040893000 + 49879296}     # profiles/r02p_mega_ring_q8_0_ncu_raw.csv (mega_ring_kernel: dram__bytes_read.sum + dram__bytes_write.sum)
